@@ -17,7 +17,7 @@ from __future__ import annotations
 from typing import Dict
 
 from ..errors import PicoError
-from ..parts.base import FixedState, PagedKV, PagedTensors
+from ..parts.base import FixedState, PagedKV, PagedLatent, PagedTensors
 
 KINDS = ("paged", "state")
 _KIND_OF: Dict[type, str] = {}
@@ -41,4 +41,5 @@ def kind_of(spec) -> str:
 
 register_cache_kind(PagedKV, "paged")
 register_cache_kind(PagedTensors, "paged")
+register_cache_kind(PagedLatent, "paged")
 register_cache_kind(FixedState, "state")

@@ -231,7 +231,9 @@ class CacheManager:
                 gi, idx = self.entry_group[eid]
                 g = self.groups[gi]
                 mine = {name: t[idx] for name, t in g.tensors.items()}
-                view = CacheView(group=gi, k=mine.get("k"), v=mine.get("v"), page_size=self.page_size, tensors=mine)
+                alias = getattr(g.spec, "kv_alias", None)     # one tensor read as keys and as values
+                view = CacheView(group=gi, k=mine.get(alias or "k"), v=mine.get(alias or "v"), page_size=self.page_size,
+                                 tensors=mine)
                 if view.k is not None and view.v is not None and view.k.is_cuda and view.k.dtype == torch.bfloat16 \
                         and view.k.dim() == 4 and view.k.shape == view.v.shape:
                     from .. import ops

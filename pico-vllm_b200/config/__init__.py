@@ -1,6 +1,7 @@
 from .base import KeyReader, read_config_json, architecture_name
 from .qwen2 import Qwen2Config
+from .zapipel import ZapipelConfig
 from .engine import EngineConfig, canonical_dtype
 
-__all__ = ["KeyReader", "read_config_json", "architecture_name", "Qwen2Config", "EngineConfig",
+__all__ = ["KeyReader", "read_config_json", "architecture_name", "Qwen2Config", "ZapipelConfig", "EngineConfig",
            "canonical_dtype"]

@@ -94,7 +94,10 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 
 def architecture_name(raw: Dict[str, Any], where: str = "config.json") -> str:
-    """The model class name config.json asks for: ``architectures[0]``."""
+    """The model class name config.json asks for: ``architectures[0]``, or the string ``architecture``."""
+    single = raw.get("architecture")
+    if "architectures" not in raw and isinstance(single, str):
+        return single
     archs = raw.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(

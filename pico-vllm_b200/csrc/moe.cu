@@ -1,0 +1,389 @@
+// Routed experts (mixture of experts): router, grouping of tokens by expert, the experts' two products as
+// grouped matrix products, and the weighted sum.  Nothing here depends on the host: a step with routed
+// experts records into a CUDA graph like any other.
+//
+//   z = W_r h + b_r                                  (float32; h in the activation type)
+//   chosen = the `top` largest z (the lower index first among equals); weight_j = softmax over the chosen z
+//   y = sum_j weight_j * W_down[e_j] ( silu(W_gate[e_j] h) * (W_up[e_j] h) )
+//
+// moe_route_kernel     one block per token: z, the choice and the weights            -> idx, wgt [T, top]
+// moe_group_kernel     one block: entries (token, j) counted and listed per expert   -> offsets [E+1], tile_start
+//                      [E+1] (64-row tiles per expert, running), perm [T*top] (place in expert order -> entry)
+// moe_gemm_*_kernel    one block per (64-row tile of one expert's entries, 64 output features): bfloat16 on
+//                      mma.sync.m16n8k16 from cp.async double-buffered tiles, or any type on the CUDA cores
+//                      (float32 models; widths that are no multiple of 8).  Epilogue GATE_UP: silu(gate) * up
+//                      into act [T*top, ff] in expert order; epilogue DOWN: float32 rows into out2 at the
+//                      entry's own place [T*top, width].
+// moe_combine_kernel   y[t] = sum_j wgt[t, j] * out2[t*top + j] in float32           -> y [T, width]
+#include "mma_helpers.cuh"
+
+#define MOE_BM 64
+#define MOE_BN 64
+#define MOE_BK 32
+#define MOE_LD (MOE_BK + 8)      // bf16 elements per shared-memory row: 80 bytes, ldmatrix rows fall in distinct banks
+
+enum { MOE_GATE_UP = 0, MOE_DOWN = 1 };
+
+template <typename TA>
+__global__ void moe_route_kernel(const TA* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
+                                 int D, int E, int top, int* __restrict__ idx, float* __restrict__ wgt) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float z[];       // E logits
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const TA* row = h + (size_t)t * D;
+    for (int e = warp; e < E; e += nw) {
+        const float* w = wr + (size_t)e * D;
+        float acc = 0.f;
+        for (int i = lane; i < D; i += 32) acc += to_f32(row[i]) * w[i];
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc + (br ? br[e] : 0.f);
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float first = 0.f, sum = 0.f, mine = 0.f;    // lane j keeps the j-th chosen logit (top <= 32)
+    int mine_e = 0;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int be = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < be)) { best = v; be = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
+        }
+        if (be == 0x7fffffff) be = 0;           // only NaN or -inf left: keep indices legal
+        if (j == 0) first = best;
+        const float p = expf(best - first);
+        sum += p;
+        if (lane == j) { mine = p; mine_e = be; }
+        __syncwarp();
+        if (lane == 0) z[be] = -INFINITY;
+        __syncwarp();
+    }
+    if (lane < top) {
+        idx[(size_t)t * top + lane] = mine_e;
+        wgt[(size_t)t * top + lane] = mine / sum;
+    }
+}
+
+// One block.  n entries (token-major: entry = t * top + j).
+__global__ void moe_group_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ offsets,
+                                 int* __restrict__ tile_start, int* __restrict__ perm) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int sm[];        // counts [E], starts [E]
+    int* counts = sm;
+    int* starts = sm + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&counts[idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = at;
+            tile_start[e] = tiles;
+            starts[e] = at;
+            at += counts[e];
+            tiles += (counts[e] + MOE_BM - 1) / MOE_BM;
+        }
+        offsets[E] = at;
+        tile_start[E] = tiles;
+    }
+    __syncthreads();
+    // the order of one expert's entries is left to the atomics: every row of a grouped product is computed by
+    // itself, so the order changes no result
+    for (int i = threadIdx.x; i < n; i += blockDim.x) perm[atomicAdd(&starts[idx[i]], 1)] = i;
+}
+
+__device__ __forceinline__ int moe_find_expert(const int* __restrict__ tile_start, int E, int tile) {
+    int lo = 0, hi = E;                 // the largest e with tile_start[e] <= tile
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_start[mid] <= tile) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float moe_silu(float g) { return g / (1.0f + expf(-g)); }
+
+// bfloat16 on tensor cores.  a: EPI GATE_UP: x [T, K] (row of entry p: perm[p] / top); EPI DOWN: act [n, K] in
+// expert order.  w: [E, NW, K] with NW = 2 * N (gate rows, then up rows) or N.  K a multiple of 8.
+template <int EPI>
+__global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w,
+                                                           const int* __restrict__ offsets,
+                                                           const int* __restrict__ tile_start,
+                                                           const int* __restrict__ perm, int E, int top, int N, int K,
+                                                           bf16* __restrict__ act, float* __restrict__ out2) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
+    __shared__ __align__(16) bf16 sa[2][MOE_BM][MOE_LD];
+    __shared__ __align__(16) bf16 sw[2][NB][MOE_BN][MOE_LD];
+    __shared__ int src_row[MOE_BM];
+    const int tile = blockIdx.x;
+    if (tile >= tile_start[E]) return;
+    const int e = moe_find_expert(tile_start, E, tile);
+    const int p0 = offsets[e] + (tile - tile_start[e]) * MOE_BM;
+    const int nrows = min(MOE_BM, offsets[e + 1] - p0);
+    const int n0 = blockIdx.y * MOE_BN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int r = tid; r < MOE_BM; r += 128)
+        src_row[r] = r < nrows ? (EPI == MOE_GATE_UP ? perm[p0 + r] / top : p0 + r) : -1;
+    __syncthreads();
+    const bf16* we = w + (size_t)e * NB * N * K;
+
+    auto load = [&](int stage, int k0) {
+        // 64 rows x 4 chunks of 8 elements each for a, the same per weight block
+#pragma unroll
+        for (int c = tid; c < MOE_BM * 4; c += 128) {
+            const int r = c >> 2, kc = (c & 3) * 8;
+            const int sr = src_row[r];
+            const bool ok = sr >= 0 && k0 + kc < K;
+            cp_async_16(smem_u32(&sa[stage][r][kc]), a + (size_t)(ok ? sr : 0) * K + (ok ? k0 + kc : 0), ok);
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int c = tid; c < MOE_BN * 4; c += 128) {
+                const int r = c >> 2, kc = (c & 3) * 8;
+                const bool ok = n0 + r < N && k0 + kc < K;
+                cp_async_16(smem_u32(&sw[stage][b][r][kc]),
+                            we + ((size_t)b * N + (ok ? n0 + r : 0)) * K + (ok ? k0 + kc : 0), ok);
+            }
+        cp_async_commit();
+    };
+
+    float acc[NB][MOE_BN / 8][4];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int j = 0; j < MOE_BN / 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[b][j][i] = 0.f;
+
+    const int nk = (K + MOE_BK - 1) / MOE_BK;
+    load(0, 0);
+    for (int kt = 0; kt < nk; ++kt) {
+        const int st = kt & 1;
+        if (kt + 1 < nk) {
+            load(st ^ 1, (kt + 1) * MOE_BK);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; kk += 16) {
+            uint32_t fa[4];
+            ldmatrix_x4(fa, smem_u32(&sa[st][warp * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int j = 0; j < MOE_BN / 8; j += 2) {
+                    uint32_t fb[4];
+                    ldmatrix_x4(fb, smem_u32(&sw[st][b][j * 8 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]));
+                    mma_bf16(acc[b][j], fa, fb[0], fb[1]);
+                    mma_bf16(acc[b][j + 1], fa, fb[2], fb[3]);
+                }
+        }
+        __syncthreads();
+    }
+    // epilogue: a thread holds rows warp*16 + lane/4 (+8) and columns j*8 + (lane%4)*2 (+1)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        if (r >= nrows) continue;
+        const int p = p0 + r;
+#pragma unroll
+        for (int j = 0; j < MOE_BN / 8; ++j) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int n = n0 + j * 8 + (lane & 3) * 2 + c;
+                if (n >= N) continue;
+                if (EPI == MOE_GATE_UP) {
+                    const float g = acc[0][j][half * 2 + c], u = acc[NB - 1][j][half * 2 + c];
+                    act[(size_t)p * N + n] = __float2bfloat16_rn(moe_silu(g) * u);
+                } else {
+                    out2[(size_t)perm[p] * N + n] = acc[0][j][half * 2 + c];
+                }
+            }
+        }
+    }
+}
+
+// Any element type on the CUDA cores, float32 accumulation: 256 threads, a 4 x 4 patch each.
+template <typename TA, int EPI>
+__global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restrict__ a, const TA* __restrict__ w,
+                                                              const int* __restrict__ offsets,
+                                                              const int* __restrict__ tile_start,
+                                                              const int* __restrict__ perm, int E, int top, int N, int K,
+                                                              TA* __restrict__ act, float* __restrict__ out2) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
+    constexpr int BK = 16;
+    __shared__ float sa[BK][MOE_BM + 4];
+    __shared__ float sw[NB][BK][MOE_BN + 4];
+    __shared__ int src_row[MOE_BM];
+    const int tile = blockIdx.x;
+    if (tile >= tile_start[E]) return;
+    const int e = moe_find_expert(tile_start, E, tile);
+    const int p0 = offsets[e] + (tile - tile_start[e]) * MOE_BM;
+    const int nrows = min(MOE_BM, offsets[e + 1] - p0);
+    const int n0 = blockIdx.y * MOE_BN;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    for (int r = tid; r < MOE_BM; r += 256)
+        src_row[r] = r < nrows ? (EPI == MOE_GATE_UP ? perm[p0 + r] / top : p0 + r) : -1;
+    __syncthreads();
+    const TA* we = w + (size_t)e * NB * N * K;
+    float acc[NB][4][4];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[b][i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int c = tid; c < MOE_BM * BK; c += 256) {
+            const int r = c / BK, k = c % BK;
+            const int sr = src_row[r];
+            sa[k][r] = (sr >= 0 && k0 + k < K) ? to_f32(a[(size_t)sr * K + k0 + k]) : 0.f;
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+            for (int c = tid; c < MOE_BN * BK; c += 256) {
+                const int r = c / BK, k = c % BK;
+                sw[b][k][r] = (n0 + r < N && k0 + k < K) ? to_f32(we[((size_t)b * N + n0 + r) * K + k0 + k]) : 0.f;
+            }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float av[4], wv[NB][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = sa[k][ty * 4 + i];
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wv[b][j] = sw[b][k][tx * 4 + j];
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[b][i][j] = fmaf(av[i], wv[b][j], acc[b][i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= nrows) continue;
+        const int p = p0 + r;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (EPI == MOE_GATE_UP)
+                act[(size_t)p * N + n] = from_f32<TA>(moe_silu(acc[0][i][j]) * acc[NB - 1][i][j]);
+            else
+                out2[(size_t)perm[p] * N + n] = acc[0][i][j];
+        }
+    }
+}
+
+template <typename TA>
+__global__ void moe_combine_kernel(const float* __restrict__ out2, const float* __restrict__ wgt, int top, int D,
+                                   size_t total, TA* __restrict__ y) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / D;
+        const int d = (int)(idx - t * D);
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) acc += wgt[t * top + j] * out2[(t * top + j) * (size_t)D + d];
+        y[idx] = from_f32<TA>(acc);
+    }
+}
+
+// h [T, D]; wr float32 [E, D]; br float32 [E] or nullptr; idx int32 [T, top]; wgt float32 [T, top].
+PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int T, int D, int E, int top, int* idx,
+                            float* wgt, int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E < 1 || top < 1 || top > E || top > 32 || E > 8192) return PICO_ERR_SIZE;
+    const size_t smem = (size_t)E * sizeof(float);
+    if (dtype == PICO_F32)
+        pico_launch((moe_route_kernel<float>), dim3(T), dim3(128), smem, stream, (const float*)h, wr, br, D, E, top, idx, wgt);
+    else if (dtype == PICO_BF16)
+        pico_launch((moe_route_kernel<bf16>), dim3(T), dim3(128), smem, stream, (const bf16*)h, wr, br, D, E, top, idx, wgt);
+    else
+        return PICO_ERR_DTYPE;
+    return pico_launch_status();
+}
+
+// The most 64-row tiles n entries over E experts can make.
+static inline int moe_max_tiles(int n, int E) { return n / MOE_BM + (n < E ? n : E); }
+
+// idx int32 [n]; offsets, tile_start int32 [E + 1]; perm int32 [n].
+PICO_API int pico_moe_group(const int* idx, int n, int E, int* offsets, int* tile_start, int* perm, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (E < 1 || E > 4096) return PICO_ERR_SIZE;
+    pico_launch(moe_group_kernel, dim3(1), dim3(256), (size_t)2 * E * sizeof(int), stream, idx, n, E, offsets, tile_start, perm);
+    return pico_launch_status();
+}
+
+// epi 0: a = x [T, K], w [E, 2N, K] -> act [n, N];  epi 1: a = act [n, K], w [E, N, K] -> out2 float32 [n, N].
+PICO_API int pico_moe_gemm(const void* a, const void* w, const int* offsets, const int* tile_start, const int* perm,
+                           int n, int E, int top, int N, int K, int epi, void* act, float* out2, int dtype,
+                           cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (N < 1 || K < 1 || (epi != MOE_GATE_UP && epi != MOE_DOWN)) return PICO_ERR_SIZE;
+    const dim3 grid(moe_max_tiles(n, E), (N + MOE_BN - 1) / MOE_BN);
+    if (grid.y > 65535) return PICO_ERR_SIZE;
+    if (dtype == PICO_BF16 && K % 8 == 0) {
+        if (epi == MOE_GATE_UP)
+            pico_launch((moe_gemm_mma_kernel<MOE_GATE_UP>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets,
+                        tile_start, perm, E, top, N, K, (bf16*)act, out2);
+        else
+            pico_launch((moe_gemm_mma_kernel<MOE_DOWN>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets,
+                        tile_start, perm, E, top, N, K, (bf16*)act, out2);
+    } else if (dtype == PICO_BF16) {
+        if (epi == MOE_GATE_UP)
+            pico_launch((moe_gemm_simple_kernel<bf16, MOE_GATE_UP>), grid, dim3(256), 0, stream, (const bf16*)a, (const bf16*)w,
+                        offsets, tile_start, perm, E, top, N, K, (bf16*)act, out2);
+        else
+            pico_launch((moe_gemm_simple_kernel<bf16, MOE_DOWN>), grid, dim3(256), 0, stream, (const bf16*)a, (const bf16*)w,
+                        offsets, tile_start, perm, E, top, N, K, (bf16*)act, out2);
+    } else if (dtype == PICO_F32) {
+        if (epi == MOE_GATE_UP)
+            pico_launch((moe_gemm_simple_kernel<float, MOE_GATE_UP>), grid, dim3(256), 0, stream, (const float*)a,
+                        (const float*)w, offsets, tile_start, perm, E, top, N, K, (float*)act, out2);
+        else
+            pico_launch((moe_gemm_simple_kernel<float, MOE_DOWN>), grid, dim3(256), 0, stream, (const float*)a,
+                        (const float*)w, offsets, tile_start, perm, E, top, N, K, (float*)act, out2);
+    } else
+        return PICO_ERR_DTYPE;
+    return pico_launch_status();
+}
+
+// out2 float32 [T * top, D]; wgt float32 [T, top]; y [T, D].
+PICO_API int pico_moe_combine(const float* out2, const float* wgt, int T, int top, int D, void* y, int dtype,
+                              cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t total = (size_t)T * D;
+    const long long cap = 16LL * pico_num_sms();
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)((long long)want > cap ? cap : (long long)want);
+    if (dtype == PICO_F32)
+        pico_launch((moe_combine_kernel<float>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (float*)y);
+    else if (dtype == PICO_BF16)
+        pico_launch((moe_combine_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (bf16*)y);
+    else
+        return PICO_ERR_DTYPE;
+    return pico_launch_status();
+}

@@ -19,6 +19,7 @@ import torch
 from .errors import KernelError
 
 _F32, _BF16 = 0, 1
+NORM_NONE, NORM_RMS, NORM_CENTRED = 0, 1, 2      # kinds of norm the row kernels have
 _lib = None
 launches = 0  # kernels of this package launched so far (graph replays add their captured count)
 
@@ -73,6 +74,14 @@ def library():
         "pico_gemm_tcgen05_pair": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
         "pico_tp_status": [vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
+        "pico_post_add_norm": [vp, vp, vp, i32, f32, vp, i32, f32, vp, vp, i32, i32, i32, vp],
+        "pico_scale_softcap": [vp, i32, i32, i32, f32, f32, vp],
+        "pico_latent_norm_store": [vp, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, vp, f32, i32, i32, vp],
+        "pico_head_scale": [vp, vp, i32, i32, i32, i32, vp],
+        "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_group": [vp, i32, i32, vp, vp, vp, vp],
+        "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_combine": [vp, vp, i32, i32, i32, vp, i32, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -694,3 +703,169 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
                                  _ptr(uniform), _ptr(out), _stream()), "sample")
     _count()
     return out
+
+
+# ------------------------------------------------------------------------------------------
+# Norm of a sublayer's output, residual add and the next norm in one kernel.
+def post_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], post_weight: Optional[torch.Tensor], post_kind: int,
+                  post_eps: float, weight: Optional[torch.Tensor], kind: int, eps: float, out: Optional[torch.Tensor],
+                  rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """x float32 [T, H] += N_post(delta) (written back unless ``rows`` picks rows), out = N(x).
+
+    ``post_kind`` / ``kind``: NORM_NONE, NORM_RMS (u / sqrt(mean u^2 + eps) * w) or NORM_CENTRED ((u - mean u) /
+    sqrt(mean (u - mean u)^2 + eps) * w); weights float32 [H].  delta (or None) and out are in the activation
+    type; with ``rows`` (int32 [R]) out[r] is computed from row rows[r] and x is left alone; ``out`` None: the add
+    alone."""
+    _cuda(x, delta, post_weight, weight, out, rows)
+    H = x.shape[1]
+    R = rows.shape[0] if rows is not None else x.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("post_add_norm: x must be contiguous float32 [T, H]")
+    for w, k, what in ((post_weight, post_kind, "post_weight"), (weight, kind, "weight")):
+        if k not in (NORM_NONE, NORM_RMS, NORM_CENTRED):
+            raise KernelError(f"post_add_norm: unknown kind of norm {k}")
+        if w is not None and (w.dtype != torch.float32 or w.shape != (H,)):
+            raise KernelError(f"post_add_norm: {what} must be float32 [H]")
+    if out is None and delta is None:
+        return None
+    like = out if out is not None else delta
+    if delta is not None and (delta.shape != x.shape or delta.dtype != like.dtype or not delta.is_contiguous()):
+        raise KernelError("post_add_norm: delta must be contiguous, shaped like x, in the activation type")
+    if out is not None and (out.shape != (R, H) or not out.is_contiguous()):
+        raise KernelError("post_add_norm: out must be contiguous [rows, H]")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("post_add_norm: rows must be int32")
+    _check(library().pico_post_add_norm(_ptr(x), _ptr(delta), _ptr(post_weight), int(post_kind), float(post_eps),
+                                        _ptr(weight), int(kind) if out is not None else NORM_NONE, float(eps), _ptr(out),
+                                        _ptr(rows), R, H, _dtype_code(like), _stream()), f"post_add_norm (width {H})")
+    _count()
+    return out
+
+
+def scale_softcap(logits: torch.Tensor, scale: float, cap: Optional[float]) -> torch.Tensor:
+    """In place on float32 logits [R, V]: y = y * scale, then y = cap * tanh(y / cap) when ``cap`` is given."""
+    _cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("scale_softcap: logits must be float32 [R, V] with contiguous rows")
+    _check(library().pico_scale_softcap(_ptr(logits), logits.shape[0], logits.shape[1], logits.stride(0), float(scale),
+                                        float(cap) if cap else 0.0, _stream()), "scale_softcap")
+    _count()
+    return logits
+
+
+# ------------------------------------------------------------------------------------------
+# Latent attention: what stands between its matrix products.
+def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, q_weight: torch.Tensor, kv_off: int, kv_rank: int,
+                      kv_weight: Optional[torch.Tensor], slots: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                      g_off: int, heads: int, eps: float):
+    """From a token's down projection row ``proj[t]`` (query latent at q_off, key/value latent at kv_off, one gate
+    logit per head at g_off): the RMS-normed query latent [T, q_rank], the RMS-normed key/value latent into cache
+    row ``slots[t]`` (``cache`` [..., row width >= kv_rank], zero beyond kv_rank; nothing for a slot of -1;
+    kv_rank 0: no key/value part), and sigmoid of the gate logits (float32 [T, heads]).  Returns (cq, gate)."""
+    _cuda(proj, q_weight, kv_weight, slots, cache)
+    T = proj.shape[0]
+    if proj.stride(1) != 1 or max(q_off + q_rank, kv_off + kv_rank, g_off + heads) > proj.shape[1]:
+        raise KernelError("latent_norm_store: the projection row is narrower than its parts")
+    if q_weight.dtype != torch.float32 or q_weight.shape != (q_rank,):
+        raise KernelError("latent_norm_store: q_weight must be float32 [q_rank]")
+    row = 0
+    if kv_rank > 0:
+        if kv_weight is None or kv_weight.dtype != torch.float32 or kv_weight.shape != (kv_rank,):
+            raise KernelError("latent_norm_store: kv_weight must be float32 [kv_rank]")
+        if slots is None or slots.dtype != torch.int32 or slots.shape[0] != T or cache is None \
+                or cache.dtype != proj.dtype or not cache.is_contiguous() or cache.shape[-1] < kv_rank:
+            raise KernelError("latent_norm_store: needs int32 slots and a contiguous cache of the activation type")
+        row = cache.shape[-1]
+    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
+    gate = torch.empty((T, heads), dtype=torch.float32, device=proj.device)
+    _check(library().pico_latent_norm_store(_ptr(proj), proj.stride(0), q_off, q_rank, _ptr(q_weight), _ptr(cq), kv_off,
+                                            kv_rank, _ptr(kv_weight), _ptr(slots), _ptr(cache) if kv_rank > 0 else None,
+                                            row, g_off, heads, _ptr(gate), float(eps), T, _dtype_code(proj), _stream()),
+           "latent_norm_store")
+    _count()
+    return cq, gate
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Per-head product: out[t, a, :] = x[t, a, :] @ weight[a] for x [T, H * K], weight [H, K, N], out [T, H * N]
+    (a strided batched library product over the heads, written straight into ``out``'s layout)."""
+    _cuda(x, weight, out)
+    T = x.shape[0]
+    H, K, N = weight.shape
+    if x.shape != (T, H * K) or out.shape != (T, H * N) or not (x.is_contiguous() and out.is_contiguous()
+                                                                and weight.is_contiguous()):
+        raise KernelError("head_linear: x [T, H K], weight [H, K, N] and out [T, H N] must be contiguous")
+    if not (x.dtype == weight.dtype == out.dtype):
+        raise KernelError("head_linear: x, weight and out must share one dtype")
+    torch.bmm(x.view(T, H, K).transpose(0, 1), weight, out=out.view(T, H, N).transpose(0, 1))
+    return out
+
+
+def head_scale(o: torch.Tensor, gate: torch.Tensor, heads: int) -> torch.Tensor:
+    """In place: o[t, h, :] *= gate[t, h] for o [T, heads * w] contiguous and gate float32 [T, heads]."""
+    _cuda(o, gate)
+    T = o.shape[0]
+    if not o.is_contiguous() or o.shape[1] % heads or gate.dtype != torch.float32 or gate.shape != (T, heads) \
+            or not gate.is_contiguous():
+        raise KernelError("head_scale: o must be contiguous [T, heads * w] and gate float32 [T, heads]")
+    _check(library().pico_head_scale(_ptr(o), _ptr(gate), T, heads, o.shape[1] // heads, _dtype_code(o), _stream()),
+           "head_scale")
+    _count()
+    return o
+
+
+# ------------------------------------------------------------------------------------------
+# Routed experts.
+def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optional[torch.Tensor], top: int):
+    """Router logits z = h W^T + b in float32, the ``top`` largest per token and the softmax over those alone.
+    h [T, D]; router_weight float32 [E, D]; router_bias float32 [E] or None.  Returns (idx int32 [T, top],
+    weights float32 [T, top])."""
+    _cuda(h, router_weight, router_bias)
+    T, D = h.shape
+    E = router_weight.shape[0]
+    if not h.is_contiguous() or router_weight.dtype != torch.float32 or router_weight.shape != (E, D) \
+            or not router_weight.is_contiguous():
+        raise KernelError("moe_route: h must be contiguous [T, D] and the router weight float32 [E, D]")
+    if router_bias is not None and (router_bias.dtype != torch.float32 or router_bias.shape != (E,)):
+        raise KernelError("moe_route: the router bias must be float32 [E]")
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    wgt = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    _check(library().pico_moe_route(_ptr(h), _ptr(router_weight), _ptr(router_bias), T, D, E, top, _ptr(idx), _ptr(wgt),
+                                    _dtype_code(h), _stream()), f"moe_route ({E} experts, top {top})")
+    _count()
+    return idx, wgt
+
+
+def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_weight: torch.Tensor,
+                down_weight: torch.Tensor) -> torch.Tensor:
+    """sum_j wgt[t, j] * down[e] (silu(gate[e] h_t) * (up[e] h_t)) with e = idx[t, j]: the (token, j) entries are
+    listed per expert on the device, the two products run as grouped products over those lists, and the weighted sum
+    is taken in float32.  gate_up_weight [E, 2 ff, D] (gate rows, then up rows), down_weight [E, D, ff], both in
+    h's type.  Returns [T, D] in h's type."""
+    _cuda(h, idx, wgt, gate_up_weight, down_weight)
+    T, D = h.shape
+    top = idx.shape[1]
+    E, ff2, _ = gate_up_weight.shape
+    ff = ff2 // 2
+    if not (h.is_contiguous() and gate_up_weight.is_contiguous() and down_weight.is_contiguous()) \
+            or gate_up_weight.shape != (E, 2 * ff, D) or down_weight.shape != (E, D, ff) \
+            or not (h.dtype == gate_up_weight.dtype == down_weight.dtype):
+        raise KernelError("moe_experts: needs contiguous h [T, D], gate_up [E, 2 ff, D] and down [E, D, ff] of one type")
+    if idx.dtype != torch.int32 or wgt.dtype != torch.float32 or idx.shape != (T, top) or wgt.shape != (T, top) \
+            or not (idx.is_contiguous() and wgt.is_contiguous()):
+        raise KernelError("moe_experts: idx int32 [T, top] and wgt float32 [T, top]")
+    n = T * top
+    lib, code, st = library(), _dtype_code(h), _stream()
+    meta = torch.empty(2 * (E + 1) + n, dtype=torch.int32, device=h.device)
+    offsets, tile_start, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
+    _check(lib.pico_moe_group(_ptr(idx), n, E, _ptr(offsets), _ptr(tile_start), _ptr(perm), st), "moe_group")
+    act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
+    _check(lib.pico_moe_gemm(_ptr(h), _ptr(gate_up_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, ff, D,
+                             0, _ptr(act), None, code, st), "moe_gemm (gate_up)")
+    out2 = torch.empty((n, D), dtype=torch.float32, device=h.device)
+    _check(lib.pico_moe_gemm(_ptr(act), _ptr(down_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, D, ff,
+                             1, None, _ptr(out2), code, st), "moe_gemm (down)")
+    y = torch.empty((T, D), dtype=h.dtype, device=h.device)
+    _check(lib.pico_moe_combine(_ptr(out2), _ptr(wgt), T, top, D, _ptr(y), code, st), "moe_combine")
+    _count(4)
+    return y

@@ -1,12 +1,15 @@
-from .base import Param, Piece, Part, PagedKV, PagedTensors, FixedState, CacheView, StepShape, MixerPlan
+from .base import Param, Piece, Part, PagedKV, PagedTensors, PagedLatent, FixedState, CacheView, StepShape, MixerPlan
 from .registry import register, make, MIXERS, FEED_FORWARDS, NORMS, POSITIONS
-from .norm import RMSNorm
+from .norm import RMSNorm, CentredNorm, NormedDelta
 from .rotary import Rotary, NoPosition
 from .attention import GQAAttention
+from .latent_attention import LatentAttention
 from .mlp import GatedMLP
+from .moe import RoutedExperts
 from .embedding import TokenEmbedding, OutputHead
-from .block import PreNormBlock
+from .block import PreNormBlock, SandwichBlock
 
 __all__ = ["Param", "Piece", "Part", "PagedKV", "PagedTensors", "FixedState", "CacheView", "StepShape", "MixerPlan", "register", "make", "MIXERS",
            "FEED_FORWARDS", "NORMS", "POSITIONS", "RMSNorm", "Rotary", "NoPosition", "GQAAttention",
-           "GatedMLP", "TokenEmbedding", "OutputHead", "PreNormBlock"]
+           "GatedMLP", "TokenEmbedding", "OutputHead", "PreNormBlock", "PagedLatent", "CentredNorm", "NormedDelta",
+           "LatentAttention", "RoutedExperts", "SandwichBlock"]

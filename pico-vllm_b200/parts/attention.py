@@ -26,6 +26,20 @@ class AttentionPlan(MixerPlan):
                                # that sees at least this many keys (two partial results per token and head in scratch)
 
 
+def decode_splits(shape: StepShape, n_kv_heads: int) -> int:
+    """How many parts to cut each single token's key range into: a power of two (the parts of one
+    token and kv head run as one thread-block cluster): up to 16 while that is at most one block
+    per SM, else up to 8 while the blocks make no more than one wave of two per SM; each part at
+    least two tiles of 64 keys."""
+    groups = max(1, shape.num_tokens * n_kv_heads)
+    want = 16 if groups * 16 <= shape.num_sms else min(2 * shape.num_sms // groups, 8)
+    want = min(want, shape.max_kv // 128)
+    splits = 1
+    while splits * 2 <= want:
+        splits *= 2
+    return splits
+
+
 @register("mixer", "gqa_attention")
 class GQAAttention(Part):
     fuses_residual = True   # forward(..., residual=x) may add its output to x and return None
@@ -65,17 +79,7 @@ class GQAAttention(Part):
         return AttentionPlan(key=(splits, pair), scratch_floats=scratch, splits=splits, pair_min_keys=pair)
 
     def _splits(self, shape: StepShape) -> int:
-        """How many parts to cut each single token's key range into: a power of two (the parts of one
-        token and kv head run as one thread-block cluster): up to 16 while that is at most one block
-        per SM, else up to 8 while the blocks make no more than one wave of two per SM; each part at
-        least two tiles of 64 keys."""
-        groups = max(1, shape.num_tokens * self.n_kv_heads)
-        want = 16 if groups * 16 <= shape.num_sms else min(2 * shape.num_sms // groups, 8)
-        want = min(want, shape.max_kv // 128)
-        splits = 1
-        while splits * 2 <= want:
-            splits *= 2
-        return splits
+        return decode_splits(shape, self.n_kv_heads)
 
     def _pair_min_keys(self, shape: StepShape) -> int:
         """Whether prompt attention should give every query tile two blocks (the threshold in keys, or 0):

@@ -73,6 +73,19 @@ class PagedTensors:
 
 
 @dataclass(frozen=True)
+class PagedLatent:
+    """The mixer keeps ONE vector of ``rank`` elements per token, which serves as key and as value of a single
+    shared key/value head: a page is [1, page_size, rank], the layout the paged attention kernels read keys and
+    values in, so the same tensor is handed to them as both (``kv_alias``).  ``window`` as in :class:`PagedKV`."""
+    rank: int
+    window: Optional[int] = None
+    kv_alias = "latent"
+
+    def page_tensors(self, page_size: int) -> Dict[str, Tuple[int, ...]]:
+        return {"latent": (1, page_size, self.rank)}
+
+
+@dataclass(frozen=True)
 class FixedState:
     """The mixer keeps one tensor of fixed shape per request (zeroed when a request starts)."""
     shape: Tuple[int, ...]

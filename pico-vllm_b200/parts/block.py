@@ -39,3 +39,30 @@ class PreNormBlock:
         if fuses:
             return part.forward(h, *args, residual=x)
         return part.forward(h, *args)
+
+
+class SandwichBlock:
+    """A layer that norms each sublayer's input and its output:  x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))).
+    ``feed_forward`` (with ``norm2`` and ``norm2b``) may be None: the layer is then its mixer alone.  A sublayer's
+    output travels on as a :class:`~pico_vllm_b200.parts.norm.NormedDelta`, so that its norm, the add and the next
+    sublayer's input norm are one kernel."""
+
+    def __init__(self, norm1: Part, mixer: Part, norm1b: Part, norm2: Optional[Part] = None,
+                 feed_forward: Optional[Part] = None, norm2b: Optional[Part] = None):
+        self.norm1, self.mixer, self.norm1b = norm1, mixer, norm1b
+        self.norm2, self.feed_forward, self.norm2b = norm2, feed_forward, norm2b
+
+    def parts(self):
+        p = {"norm1": self.norm1, "mixer": self.mixer, "norm1b": self.norm1b}
+        if self.feed_forward is not None:
+            p.update(norm2=self.norm2, feed_forward=self.feed_forward, norm2b=self.norm2b)
+        return p
+
+    def forward(self, x: torch.Tensor, pending, batch, cache: CacheView):
+        from .norm import NormedDelta
+        h = self.norm1.add_norm(x, pending)
+        pending = NormedDelta(self.mixer.forward(h, batch, cache), self.norm1b)
+        if self.feed_forward is None:
+            return x, pending
+        h = self.norm2.add_norm(x, pending)
+        return x, NormedDelta(self.feed_forward.forward(h, batch), self.norm2b)

@@ -30,8 +30,12 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
-    def __init__(self, vocab: int, width: int, tied_to: Optional[TokenEmbedding] = None):
+    def __init__(self, vocab: int, width: int, tied_to: Optional[TokenEmbedding] = None, logit_scale: float = 1.0,
+                 softcap: Optional[float] = None):
+        """``logit_scale`` and ``softcap``: logits = softcap * tanh(logit_scale * (y . W^T) / softcap) (no cap
+        when ``softcap`` is None), float32, in one kernel after the product."""
         self.vocab, self.width, self.tied_to = vocab, width, tied_to
+        self.logit_scale, self.softcap = float(logit_scale), softcap
         self.weight = None
 
     def params(self) -> List[Param]:
@@ -42,8 +46,13 @@ class OutputHead(Part):
     def matrix(self) -> torch.Tensor:
         return self.tied_to.weight if self.tied_to is not None else self.weight
 
+    def _shape(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.logit_scale != 1.0 or self.softcap:
+            ops.scale_softcap(logits, self.logit_scale, self.softcap)
+        return logits
+
     def forward(self, y: torch.Tensor) -> torch.Tensor:
-        return ops.logits_linear(y, self.matrix())
+        return self._shape(ops.logits_linear(y, self.matrix()))
 
     def can_fuse_norm(self, x: torch.Tensor, norm, n_rows: int) -> bool:
         return getattr(norm, "plain_rms", False) and getattr(norm, "weight", None) is not None \
@@ -51,7 +60,7 @@ class OutputHead(Part):
 
     def forward_normed(self, x: torch.Tensor, norm, rows: torch.Tensor) -> torch.Tensor:
         """Logits of rows ``rows`` of the residual stream x, with the last norm applied inside the kernel."""
-        return ops.skinny_linear(x, self.matrix(), None, torch.float32, norm.weight, norm.eps, rows)
+        return self._shape(ops.skinny_linear(x, self.matrix(), None, torch.float32, norm.weight, norm.eps, rows))
 
     def greedy(self, x: torch.Tensor, norm, rows: Optional[torch.Tensor], n_rows: int, out: torch.Tensor) -> bool:
         """The greedy tokens of ``n_rows`` rows straight into ``out`` (int32), without logits: argmax in the
@@ -59,6 +68,8 @@ class OutputHead(Part):
         (``rows`` picks its rows); without, x is already normed.  False when the fused kernel does not take
         the sizes: the caller then computes logits."""
         w = self.matrix()
+        if not self.logit_scale > 0.0:      # a positive scale and the cap keep the order of the logits; anything else does not
+            return False
         if norm is not None:
             if not self.can_fuse_norm(x, norm, n_rows):
                 return False

@@ -1,4 +1,8 @@
-"""RMS norm on the float32 residual stream, fused with the residual add that precedes it.
+"""Norms on the float32 residual stream, fused with the residual add that precedes them.
+
+:class:`RMSNorm` and :class:`CentredNorm` (mean taken off, weight, no bias).  What is added may itself be normed
+first (:class:`NormedDelta`: a sublayer's output with the norm that stands between it and the stream): norm,
+add and the next norm are then one kernel.
 
 y = x * rsqrt(mean(x^2) + eps) * w in float32 (pico_vllm/RMSNorm.py:22-34; plain form
 pico_vllm/model.py:57-66).  The reference adds the residual in a separate torch op
@@ -6,7 +10,8 @@ pico_vllm/model.py:57-66).  The reference adds the residual in a separate torch 
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from dataclasses import dataclass
+from typing import List, Optional, Union
 
 import torch
 
@@ -15,11 +20,29 @@ from .base import Param, Part, Piece
 from .registry import register
 
 
+@dataclass
+class NormedDelta:
+    """A sublayer's output that is still to pass through ``norm`` before it is added to the residual stream."""
+    delta: torch.Tensor
+    norm: "Part"
+
+
+def _post_add_norm(norm, kind: int, x: torch.Tensor, delta, rows: Optional[torch.Tensor]) -> torch.Tensor:
+    n = rows.shape[0] if rows is not None else x.shape[0]
+    out = torch.empty((n, norm.width), dtype=norm.act_dtype, device=x.device)
+    post = None
+    if isinstance(delta, NormedDelta):
+        post, delta = delta.norm, delta.delta
+    return ops.post_add_norm(x, delta, None if post is None else post.weight, 0 if post is None else post.norm_kind,
+                             0.0 if post is None else post.eps, norm.weight, kind, norm.eps, out, rows)
+
+
 @register("norm", "rmsnorm")
 class RMSNorm(Part):
     # y = x * rsqrt(mean(x^2) + eps) * weight and nothing else: what the product kernels with the norm inside
     # compute.  A part that takes a norm into its own kernel asks for this mark, not for attribute names.
     plain_rms = True
+    norm_kind = ops.NORM_RMS
 
     def __init__(self, width: int, eps: float):
         self.width, self.eps = width, eps
@@ -36,6 +59,31 @@ class RMSNorm(Part):
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: float32 [T, width] residual stream, updated in place by ``x += delta`` unless
         ``rows`` picks rows (then x stays).  Returns norm(x) in the activation dtype."""
+        if isinstance(delta, NormedDelta):
+            return _post_add_norm(self, ops.NORM_RMS, x, delta, rows)
         n = rows.shape[0] if rows is not None else x.shape[0]
         out = torch.empty((n, self.width), dtype=self.act_dtype, device=x.device)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+
+
+@register("norm", "centred_norm")
+class CentredNorm(Part):
+    """y = (x - mean x) / sqrt(mean((x - mean x)^2) + eps) * weight: a layer norm with a weight and no bias,
+    float32 throughout."""
+    norm_kind = ops.NORM_CENTRED
+
+    def __init__(self, width: int, eps: float):
+        self.width, self.eps = width, eps
+        self.weight: Optional[torch.Tensor] = None
+        self.act_dtype = torch.bfloat16
+
+    def params(self) -> List[Param]:
+        return [Param("weight", (Piece("weight", (self.width,)),), kind="vector", init="one_plus_normal")]
+
+    def materialize(self, device, dtype):
+        self.act_dtype = dtype
+
+    def add_norm(self, x: torch.Tensor, delta: Union[None, torch.Tensor, NormedDelta],
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """As :meth:`RMSNorm.add_norm`; ``delta`` may be a :class:`NormedDelta`."""
+        return _post_add_norm(self, ops.NORM_CENTRED, x, delta, rows)

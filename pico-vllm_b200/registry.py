@@ -42,6 +42,9 @@ def _register_builtin() -> None:
     from .config.qwen2 import Qwen2Config
     from .models.qwen2 import build_qwen2
     register_architecture("Qwen2ForCausalLM", Qwen2Config, build_qwen2)
+    from .config.zapipel import ZapipelConfig
+    from .models.zapipel import build_zapipel
+    register_architecture("Zapipel", ZapipelConfig, build_zapipel)
 
 
 _register_builtin()
