@@ -59,6 +59,16 @@ def route(h, w_router, b_router, top):
     return idx, torch.softmax(val, dim=-1)
 
 
+def route_margin(h, w_router, b_router, top):
+    """How far each token is from another choice of experts: (smallest chosen logit - largest logit not chosen)
+    over the largest |logit|; infinite when every expert is chosen."""
+    z = h @ w_router.T + b_router
+    val, _ = torch.sort(z, dim=-1, descending=True)
+    if top >= z.shape[-1]:
+        return torch.full(z.shape[:-1], float("inf"), dtype=z.dtype)
+    return (val[:, top - 1] - val[:, top]) / z.abs().amax(-1)
+
+
 def moe_ff(h, p, experts, top):
     idx, wgt = route(h, p["router"], p["router.b"], top)
     out = torch.zeros_like(h)
@@ -72,7 +82,7 @@ def moe_ff(h, p, experts, top):
 
 def head_logits(x, w_norm, w_head, eps, logit_scale, softcap):
     y = layer_norm(x, w_norm, eps) @ w_head.T * logit_scale
-    return softcap * torch.tanh(y / softcap)
+    return y if softcap is None else softcap * torch.tanh(y / softcap)
 
 
 def _sub(tensors, prefix):
@@ -89,7 +99,7 @@ class PlainZapipel:
         self.dtype = dtype
 
     def new_state(self):
-        return {"len": 0, "latents": {}}        # layer index -> [len, R]
+        return {"len": 0, "latents": {}, "margin": []}        # latents: layer index -> [len, R]; margin: per position
 
     def forward(self, state, tokens, keep_layers=False):
         """Feeds the next tokens of one sequence; returns logits [T, vocab] (and, on request, the residual
@@ -98,6 +108,7 @@ class PlainZapipel:
         x = t["embed"][torch.as_tensor(tokens, dtype=torch.long)]
         start = state["len"]
         after = []
+        margin = torch.full((len(tokens),), float("inf"), dtype=self.dtype)
         for i, layer in enumerate(cfg["layers"]):
             assert layer["type"] == "latent_attention"
             m = layer["mixer"]
@@ -121,10 +132,12 @@ class PlainZapipel:
                     y = dense_ff(h, pf)
                 else:
                     y = moe_ff(h, pf, ff["router"]["experts"], ff["router"]["top"])
+                    margin = torch.minimum(margin, route_margin(h, pf["router"], pf["router.b"], ff["router"]["top"]))
                 x = x + layer_norm(y, t[pre + "norm2b"], eps)
             after.append(x.clone())
         state["len"] = start + len(tokens)
-        logits = head_logits(x, t["final.norm"], t["head"], eps, float(cfg["logit_scale"]), float(cfg["logit_softcap"]))
+        state["margin"] += margin.tolist()
+        logits = head_logits(x, t["final.norm"], t["head"], eps, float(cfg.get("logit_scale", 1.0)), cfg.get("logit_softcap"))
         return (logits, after) if keep_layers else logits
 
     def greedy(self, prompt, n_new):
