@@ -536,6 +536,78 @@ def run_shape(args):
     return 0
 
 
+# --design zapipel: the latent-attention design beside the Qwen2 decoder at equal sizes (width, layers, heads, head
+# size, vocabulary; the feed-forward's active size: a routed layer's `top` experts together are as wide as the dense
+# feed-forward).  Even layers keep their own latents and have a dense feed-forward, odd layers read the latents of the
+# layer before and have routed experts.
+DESIGN_SHAPES = {
+    "1536": dict(width=1536, heads=12, kv_heads=2, head=128, q_rank=768, kv_rank=128, ff=8960, experts=16, top=4),
+    "2048": dict(width=2048, heads=16, kv_heads=2, head=128, q_rank=1024, kv_rank=128, ff=11008, experts=32, top=4),
+}
+DESIGN_VOCAB = 32000
+
+
+def design_configs(shape, layers):
+    s = DESIGN_SHAPES[shape]
+    mixer = dict(heads=s["heads"], dim=s["head"], vdim=s["head"], q_rank=s["q_rank"], kv_rank=s["kv_rank"],
+                 scale=s["head"] ** -0.5)
+    zl = []
+    for i in range(layers):
+        if i % 2 == 0:
+            zl.append(dict(type="latent_attention", mixer=dict(mixer), mlp=dict(kind="dense", ff=s["ff"])))
+        else:
+            zl.append(dict(type="latent_attention", mixer=dict(mixer, kv_from=i - 1),
+                           mlp=dict(kind="moe", expert=dict(ff=s["ff"] // s["top"]),
+                                    router=dict(experts=s["experts"], top=s["top"]))))
+    zap = dict(architecture="Zapipel", vocab=DESIGN_VOCAB, width=s["width"], norm=dict(eps=1e-5), logit_scale=1.0,
+               logit_softcap=30.0, layers=zl)
+    qwen = dict(MODEL, vocab_size=DESIGN_VOCAB, hidden_size=s["width"], num_hidden_layers=layers,
+                num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["head"],
+                intermediate_size=s["ff"], tie_word_embeddings=False)
+    return {"zapipel": zap, "qwen2": qwen}
+
+
+def run_design(args):
+    """Prefill (one 2,048-token prompt) and decode (``--batch`` requests at ``--context``; default 8 and 64 at
+    2,048) of the Zapipel design and of the Qwen2 decoder at equal sizes, random weights drawn on the device.
+    Prints one JSON line; with ``--only`` and ``--arch`` one phase of one model (for a launch list)."""
+    import torch
+    import pico_vllm_b200  # noqa: F401
+    from pico_vllm_b200 import LLM
+    pk = peaks()
+    layers = args.layers or 8
+    context = args.context or 2048
+    batches = [args.batch] if args.batch else [8, 64]
+    shapes = sorted(DESIGN_SHAPES) if args.shape == "all" else [args.shape]
+    archs = ["zapipel", "qwen2"] if args.arch == "both" else [args.arch]
+    out = {"design": "zapipel", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+           "layers": layers, "vocab": DESIGN_VOCAB, "context": context, "peaks": pk["source"], "shapes": {}}
+    sampler = ClockSampler()
+    sampler.start()
+    for shape in shapes:
+        res = out["shapes"][shape] = {"sizes": DESIGN_SHAPES[shape]}
+        for arch in archs:
+            cfg, model = random_model_on_device(design_configs(shape, layers)[arch])
+            max_b = max(batches)
+            llm = LLM(model, dtype="bfloat16", page_size=16, num_pages=max_b * (context // 16 + 2) + 256, max_num_seqs=max_b,
+                      max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=context + 64, use_cuda_graph=True)
+            r = res[arch] = {"weight_GB": round(weight_bytes(llm.model) / 1e9, 3),
+                             "cache_bytes_per_token": kv_bytes_per_token(llm.model, llm.cache)}
+            if args.only != "decode":
+                ms = prefill_phase(llm, 2048, reps=2 if args.only else 5, seed=3)
+                r["prefill_2048"] = {"ms": round(ms, 3), "tok_s": round(2048 / ms * 1e3)}
+            if args.only != "prefill":
+                for b in batches:
+                    ms, launches = decode_phase(llm, b, context, args.steps, args.warmup, seed=1)
+                    r[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tok_s": round(b / ms * 1e3),
+                                         "launches_per_step": round(launches, 1)}
+            del llm, model
+            torch.cuda.empty_cache()
+    out["clocks"] = sampler.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
     import torch
     if not torch.cuda.is_available():
@@ -646,6 +718,10 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase only and print a short line (for profiling; not a bench value)")
+    ap.add_argument("--design", choices=["zapipel"], default=None,
+                    help="the named design beside the Qwen2 decoder at equal sizes (prefill and decode); not the default run")
+    ap.add_argument("--shape", choices=sorted(DESIGN_SHAPES) + ["all"], default="all", help="with --design: which sizes")
+    ap.add_argument("--arch", choices=["zapipel", "qwen2", "both"], default="both", help="with --design: which model")
     ap.add_argument("--micro", action="store_true",
                     help="time single decode kernels replayed from a graph (skinny products, decode attention)")
     ap.add_argument("--profile-range", choices=["decode", "prefill"], default=None,
@@ -655,6 +731,14 @@ def main():
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (this engine runs on a single GPU)")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has the Qwen2.5-1.5B shape only "
+                                                                  "(pico_vllm/model.py:15-26)"}))
+            return 0
+        global PROFILE_RANGE
+        PROFILE_RANGE = args.profile_range
+        return run_design(args)
     if args.config == "1.5b" or args.micro:
         args.layers = args.layers or FULL_LAYERS
         args.batch = args.batch or 8
@@ -677,7 +761,6 @@ def main():
                                     head_dim=MODEL["hidden_size"] // MODEL["num_attention_heads"])
             return prefill_flops(shape, T)
         return run_reference(args, peaks(), ClockSampler(), flops, PUBLISHED_DECODE_B1)
-    global PROFILE_RANGE
     PROFILE_RANGE = args.profile_range
     if args.only:
         args.no_points = True

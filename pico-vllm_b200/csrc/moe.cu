@@ -24,30 +24,66 @@
 
 enum { MOE_GATE_UP = 0, MOE_DOWN = 1 };
 
-template <typename TA>
-__global__ void moe_route_kernel(const TA* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br,
-                                 int D, int E, int top, int* __restrict__ idx, float* __restrict__ wgt) {
+// TOK tokens per block (their rows of h in shared memory as float32, so that a warp reads an expert's router row once
+// for all of them); 8 warps take the experts in turn; warp w < TOK then chooses for token w.
+template <typename TA, int TOK>
+__global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h, const float* __restrict__ wr,
+                                                        const float* __restrict__ br, int T, int D, int E, int top,
+                                                        int* __restrict__ idx, float* __restrict__ wgt) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float z[];       // E logits
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const TA* row = h + (size_t)t * D;
-    for (int e = warp; e < E; e += nw) {
-        const float* w = wr + (size_t)e * D;
-        float acc = 0.f;
-        for (int i = lane; i < D; i += 32) acc += to_f32(row[i]) * w[i];
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc + (br ? br[e] : 0.f);
+    extern __shared__ __align__(16) float rsm[];       // TOK rows of D floats (D rounded up to 4), then TOK x E logits
+    const int Dp = (D + 3) & ~3;
+    float* hs = rsm;
+    float* z = rsm + TOK * Dp;
+    const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int nt = min(TOK, T - t0);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < TOK * D; i += blockDim.x) {
+        const int k = i / D, d = i - k * D;
+        hs[k * Dp + d] = k < nt ? to_f32(h[(size_t)(t0 + k) * D + d]) : 0.f;
     }
     __syncthreads();
-    if (warp != 0) return;
+    const bool vec = (D & 3) == 0;
+    for (int e = warp; e < E; e += nw) {
+        const float* w = wr + (size_t)e * D;
+        float acc[TOK];
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) acc[k] = 0.f;
+        if (vec) {
+#pragma unroll 4
+            for (int i = lane * 4; i < D; i += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + i);
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) {
+                    const float4 hv = *reinterpret_cast<const float4*>(hs + k * Dp + i);
+                    acc[k] += (hv.x * wv.x + hv.y * wv.y) + (hv.z * wv.z + hv.w * wv.w);
+                }
+            }
+        } else {
+            for (int i = lane; i < D; i += 32) {
+                const float wv = w[i];
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) acc[k] += hs[k * Dp + i] * wv;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) {
+            const float a = warp_sum(acc[k]);
+            if (lane == 0) z[k * E + e] = a + (br ? br[e] : 0.f);
+        }
+    }
+    __syncthreads();
+    if (warp >= nt) return;
+    float* zt = z + warp * E;
+    const int t = t0 + warp;
     float first = 0.f, sum = 0.f, mine = 0.f;    // lane j keeps the j-th chosen logit (top <= 32)
     int mine_e = 0;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
         int be = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
+            const float v = zt[e];
             if (v > best || (v == best && e < be)) { best = v; be = e; }
         }
 #pragma unroll
@@ -62,7 +98,7 @@ __global__ void moe_route_kernel(const TA* __restrict__ h, const float* __restri
         sum += p;
         if (lane == j) { mine = p; mine_e = be; }
         __syncwarp();
-        if (lane == 0) z[be] = -INFINITY;
+        if (lane == 0) zt[be] = -INFINITY;
         __syncwarp();
     }
     if (lane < top) {
@@ -73,7 +109,7 @@ __global__ void moe_route_kernel(const TA* __restrict__ h, const float* __restri
 
 // One block.  n entries (token-major: entry = t * top + j).
 __global__ void moe_group_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ offsets,
-                                 int* __restrict__ tile_start, int* __restrict__ perm) {
+                                 int* __restrict__ tile_start, int* __restrict__ perm, int* __restrict__ place) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ int sm[];        // counts [E], starts [E]
@@ -98,7 +134,11 @@ __global__ void moe_group_kernel(const int* __restrict__ idx, int n, int E, int*
     __syncthreads();
     // the order of one expert's entries is left to the atomics: every row of a grouped product is computed by
     // itself, so the order changes no result
-    for (int i = threadIdx.x; i < n; i += blockDim.x) perm[atomicAdd(&starts[idx[i]], 1)] = i;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int p = atomicAdd(&starts[idx[i]], 1);
+        perm[p] = i;
+        if (place) place[i] = p;
+    }
 }
 
 __device__ __forceinline__ int moe_find_expert(const int* __restrict__ tile_start, int E, int tile) {
@@ -316,13 +356,24 @@ PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int
                             float* wgt, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E < 1 || top < 1 || top > E || top > 32 || E > 8192) return PICO_ERR_SIZE;
-    const size_t smem = (size_t)E * sizeof(float);
-    if (dtype == PICO_F32)
-        pico_launch((moe_route_kernel<float>), dim3(T), dim3(128), smem, stream, (const float*)h, wr, br, D, E, top, idx, wgt);
-    else if (dtype == PICO_BF16)
-        pico_launch((moe_route_kernel<bf16>), dim3(T), dim3(128), smem, stream, (const bf16*)h, wr, br, D, E, top, idx, wgt);
-    else
+    // four tokens a block when there are many (the router matrix is read once per block), one otherwise
+    const int tok = T >= 512 ? 4 : 1;
+    const size_t smem = ((size_t)tok * ((D + 3) & ~3) + (size_t)tok * E) * sizeof(float);
+    if (smem > 200 * 1024) return PICO_ERR_SIZE;
+    const dim3 grid((T + tok - 1) / tok);
+#define LAUNCH_ROUTE(TA, TOK)                                                                                             \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024)                                                                                             \
+            cudaFuncSetAttribute(moe_route_kernel<TA, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        pico_launch((moe_route_kernel<TA, TOK>), grid, dim3(256), smem, stream, (const TA*)h, wr, br, T, D, E, top, idx, wgt); \
+    } while (0)
+    if (dtype == PICO_F32) {
+        if (tok == 4) LAUNCH_ROUTE(float, 4); else LAUNCH_ROUTE(float, 1);
+    } else if (dtype == PICO_BF16) {
+        if (tok == 4) LAUNCH_ROUTE(bf16, 4); else LAUNCH_ROUTE(bf16, 1);
+    } else
         return PICO_ERR_DTYPE;
+#undef LAUNCH_ROUTE
     return pico_launch_status();
 }
 
@@ -330,10 +381,99 @@ PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int
 static inline int moe_max_tiles(int n, int E) { return n / MOE_BM + (n < E ? n : E); }
 
 // idx int32 [n]; offsets, tile_start int32 [E + 1]; perm int32 [n].
-PICO_API int pico_moe_group(const int* idx, int n, int E, int* offsets, int* tile_start, int* perm, cudaStream_t stream) {
+PICO_API int pico_moe_group(const int* idx, int n, int E, int* offsets, int* tile_start, int* perm, int* place,
+                            cudaStream_t stream) {
     if (n <= 0) return 0;
     if (E < 1 || E > 4096) return PICO_ERR_SIZE;
-    pico_launch(moe_group_kernel, dim3(1), dim3(256), (size_t)2 * E * sizeof(int), stream, idx, n, E, offsets, tile_start, perm);
+    pico_launch(moe_group_kernel, dim3(1), dim3(n >= 4096 ? 1024 : 256), (size_t)2 * E * sizeof(int), stream, idx, n, E,
+                offsets, tile_start, perm, place);
+    return pico_launch_status();
+}
+
+// The library path for many tokens: rows gathered into expert order, a library grouped product on them, and the
+// weighted sum read back through ``place``.
+// xs[p, :] = x[perm[p] / top, :], 16 bytes per thread and access (D * sizeof a multiple of 16).
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ perm, int top, int row16,
+                                  size_t total, uint4* __restrict__ xs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = idx / row16;
+        const int c = (int)(idx - p * row16);
+        xs[idx] = x[(size_t)(perm[p] / top) * row16 + c];
+    }
+}
+
+PICO_API int pico_moe_gather(const void* x, const int* perm, int n, int top, int row_bytes, void* xs, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (row_bytes % 16 != 0 || top < 1) return PICO_ERR_ALIGN;
+    const size_t total = (size_t)n * (row_bytes / 16);
+    const long long cap = 16LL * pico_num_sms();
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)((long long)want > cap ? cap : (long long)want);
+    pico_launch(moe_gather_kernel, dim3(blocks), dim3(256), 0, stream, (const uint4*)x, perm, top, row_bytes / 16, total,
+                (uint4*)xs);
+    return pico_launch_status();
+}
+
+// y[t] = sum_j wgt[t, j] * ys[place[t * top + j]] with ys in expert order (activation type), float32 sum.
+// VEC: D a multiple of 8 (bfloat16) or 4 (float32): 16 bytes per access.
+template <typename TA, bool VEC>
+__global__ void moe_combine_placed_kernel(const TA* __restrict__ ys, const int* __restrict__ place,
+                                          const float* __restrict__ wgt, int top, int D, size_t total, TA* __restrict__ y) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int W = VEC ? 16 / (int)sizeof(TA) : 1;
+    const int Dv = D / W;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / Dv;
+        const int d = (int)(idx - t * Dv) * W;
+        float acc[W];
+#pragma unroll
+        for (int k = 0; k < W; ++k) acc[k] = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const float g = wgt[t * top + j];
+            const TA* row = ys + (size_t)place[t * top + j] * D + d;
+            if (VEC) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(row);
+                const TA* v = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+                for (int k = 0; k < W; ++k) acc[k] += g * to_f32(v[k]);
+            } else {
+                acc[0] += g * to_f32(row[0]);
+            }
+        }
+        if (VEC) {
+            uint4 raw;
+            TA* v = reinterpret_cast<TA*>(&raw);
+#pragma unroll
+            for (int k = 0; k < W; ++k) v[k] = from_f32<TA>(acc[k]);
+            *reinterpret_cast<uint4*>(y + t * (size_t)D + d) = raw;
+        } else {
+            y[t * (size_t)D + d] = from_f32<TA>(acc[0]);
+        }
+    }
+}
+
+PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const float* wgt, int T, int top, int D, void* y,
+                                     int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dtype != PICO_F32 && dtype != PICO_BF16) return PICO_ERR_DTYPE;
+    const int w = dtype == PICO_F32 ? 4 : 8;
+    const bool vec = D % w == 0;
+    const size_t total = (size_t)T * (vec ? D / w : D);
+    const long long cap = 16LL * pico_num_sms();
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)((long long)want > cap ? cap : (long long)want);
+#define LAUNCH_CP(TA, V)                                                                                              \
+    pico_launch((moe_combine_placed_kernel<TA, V>), dim3(blocks), dim3(256), 0, stream, (const TA*)ys, place, wgt, top, D, \
+                total, (TA*)y)
+    if (dtype == PICO_F32) {
+        if (vec) LAUNCH_CP(float, true); else LAUNCH_CP(float, false);
+    } else {
+        if (vec) LAUNCH_CP(bf16, true); else LAUNCH_CP(bf16, false);
+    }
+#undef LAUNCH_CP
     return pico_launch_status();
 }
 

@@ -79,7 +79,9 @@ def library():
         "pico_latent_norm_store": [vp, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, vp, f32, i32, i32, vp],
         "pico_head_scale": [vp, vp, i32, i32, i32, i32, vp],
         "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp],
-        "pico_moe_group": [vp, i32, i32, vp, vp, vp, vp],
+        "pico_moe_group": [vp, i32, i32, vp, vp, vp, vp, vp],
+        "pico_moe_gather": [vp, vp, i32, i32, i32, vp, vp],
+        "pico_moe_combine_placed": [vp, vp, vp, i32, i32, i32, vp, i32, vp],
         "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
         "pico_moe_combine": [vp, vp, i32, i32, i32, vp, i32, vp],
     }
@@ -856,16 +858,44 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
         raise KernelError("moe_experts: idx int32 [T, top] and wgt float32 [T, top]")
     n = T * top
     lib, code, st = library(), _dtype_code(h), _stream()
-    meta = torch.empty(2 * (E + 1) + n, dtype=torch.int32, device=h.device)
-    offsets, tile_start, perm = meta[:E + 1], meta[E + 1:2 * (E + 1)], meta[2 * (E + 1):]
-    _check(lib.pico_moe_group(_ptr(idx), n, E, _ptr(offsets), _ptr(tile_start), _ptr(perm), st), "moe_group")
+    grouped = moe_library_takes(h, n, D, ff)
+    meta = torch.empty(2 * (E + 1) + 2 * n, dtype=torch.int32, device=h.device)
+    offsets, tile_start = meta[:E + 1], meta[E + 1:2 * (E + 1)]
+    perm, place = meta[2 * (E + 1):2 * (E + 1) + n], meta[2 * (E + 1) + n:]
+    _check(lib.pico_moe_group(_ptr(idx), n, E, _ptr(offsets), _ptr(tile_start), _ptr(perm),
+                              _ptr(place) if grouped else None, st), "moe_group")
+    y = torch.empty((T, D), dtype=h.dtype, device=h.device)
+    if grouped:
+        # many tokens: rows in expert order, the library's grouped products (their group ends are read on the device),
+        # the activation kernel between them
+        xs = torch.empty((n, D), dtype=h.dtype, device=h.device)
+        _check(lib.pico_moe_gather(_ptr(h), _ptr(perm), n, top, D * h.element_size(), _ptr(xs), st), "moe_gather")
+        _count(2)
+        ends = offsets[1:]
+        gu = torch._grouped_mm(xs, gate_up_weight.transpose(1, 2), offs=ends)
+        act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
+        swiglu(gu, act)
+        ys = torch._grouped_mm(act, down_weight.transpose(1, 2), offs=ends)
+        _check(lib.pico_moe_combine_placed(_ptr(ys), _ptr(place), _ptr(wgt), T, top, D, _ptr(y), code, st),
+               "moe_combine_placed")
+        _count()
+        return y
     act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(h), _ptr(gate_up_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, ff, D,
                              0, _ptr(act), None, code, st), "moe_gemm (gate_up)")
     out2 = torch.empty((n, D), dtype=torch.float32, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(act), _ptr(down_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, D, ff,
                              1, None, _ptr(out2), code, st), "moe_gemm (down)")
-    y = torch.empty((T, D), dtype=h.dtype, device=h.device)
     _check(lib.pico_moe_combine(_ptr(out2), _ptr(wgt), T, top, D, _ptr(y), code, st), "moe_combine")
     _count(4)
     return y
+
+
+MOE_LIBRARY_MIN_ROWS = 1024       # (token, expert) pairs from which the library's grouped product is used
+
+
+def moe_library_takes(h: torch.Tensor, n: int, D: int, ff: int) -> bool:
+    """Whether the experts' products go to the library's grouped matrix product (bfloat16, many rows, row sizes
+    that are multiples of 16 bytes) instead of this package's grouped kernels."""
+    return (h.dtype == torch.bfloat16 and n >= MOE_LIBRARY_MIN_ROWS and D % 8 == 0 and ff % 8 == 0
+            and hasattr(torch, "_grouped_mm"))

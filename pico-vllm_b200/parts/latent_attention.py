@@ -37,6 +37,13 @@ def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m
 
 
+def _linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """A handful of tokens: the weight-streaming kernel; more: the library product."""
+    if ops.skinny_takes(x, weight):
+        return ops.skinny_linear(x, weight)
+    return ops.linear(x, weight)
+
+
 @register("mixer", "latent_attention")
 class LatentAttention(Part):
     def __init__(self, width: int, heads: int, dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float, eps: float,
@@ -99,13 +106,13 @@ class LatentAttention(Part):
         T, H, R = h.shape[0], self.heads, self.row
         latent = cache.tensors["latent"]                       # [pages, 1, page_size, R]
         stores = self.own_latent and cache.store
-        proj = ops.linear(h, self.down_weight)
+        proj = _linear(h, self.down_weight)
         kv_off = self.q_rank
         g_off = self.q_rank + (self.kv_rank if self.own_latent else 0)
         cq, gate = ops.latent_norm_store(proj, 0, self.q_rank, self.q_norm, kv_off, self.kv_rank if stores else 0,
                                          self.kv_norm if stores else None, gb.slots if stores else None,
                                          latent if stores else None, g_off, H, self.eps)
-        q = ops.linear(cq, self.uq_weight)                      # [T, H d]
+        q = _linear(cq, self.uq_weight)                         # [T, H d]
         qa = torch.empty((T, H * R), dtype=h.dtype, device=h.device)
         ops.head_linear(q, self.uk_weight, qa)                  # q'_a = W_uk[a]^T q_a
         oa = torch.empty((T, H * R), dtype=h.dtype, device=h.device)
@@ -122,4 +129,4 @@ class LatentAttention(Part):
         o = torch.empty((T, H * self.vdim), dtype=h.dtype, device=h.device)
         ops.head_linear(oa, self.uv_weight, o)                  # o_a = W_uv[a] o'_a
         ops.head_scale(o, gate, H)
-        return ops.linear(o, self.o_weight)
+        return _linear(o, self.o_weight)

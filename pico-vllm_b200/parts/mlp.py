@@ -54,4 +54,6 @@ class GatedMLP(Part):
         if residual is not None and ops.skinny_takes(a, self.down_weight):
             ops.skinny_linear_residual(a, self.down_weight, residual)
             return None
+        if ops.skinny_takes(a, self.down_weight):
+            return ops.skinny_linear(a, self.down_weight)
         return ops.linear(a, self.down_weight)

@@ -246,7 +246,7 @@ def test_long_decoding_and_reused_slots(dtype):
 
 # ------------------------------------------------------------------ kernels alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [96, 130, 1000])
+@pytest.mark.parametrize("width", [96, 130, 1000, 1536, 2048, 2304])
 def test_norm_add_norm_kernel(dtype, width):
     from pico_vllm_b200 import ops
     g = torch.Generator().manual_seed(width)
@@ -312,10 +312,12 @@ def test_latent_norm_store_kernel(dtype):
 
 
 @pytest.mark.parametrize("experts,top", [(5, 1), (12, 3), (40, 8), (3, 3)])
-def test_router_kernel(experts, top):
+@pytest.mark.parametrize("T,D", [(50, 72), (701, 72), (9, 70), (600, 50)])
+def test_router_kernel(experts, top, T, D):
+    """Few tokens (a block per token) and many (four per block, the last block not full); widths that are and are
+    not a multiple of 4."""
     from pico_vllm_b200 import ops
-    g = torch.Generator().manual_seed(experts)
-    T, D = 50, 72
+    g = torch.Generator().manual_seed(experts + T)
     h = torch.randn(T, D, generator=g).to(torch.bfloat16)
     w, b = torch.randn(experts, D, generator=g), torch.randn(experts, generator=g) * 2
     for x in (h, h.float()):
@@ -329,10 +331,11 @@ def test_router_kernel(experts, top):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,D,ff,experts,top", [(1, 64, 32, 4, 2), (150, 96, 40, 6, 2), (300, 72, 24, 3, 1),
-                                                (70, 100, 36, 5, 5), (33, 60, 20, 7, 3)])
+                                                (70, 100, 36, 5, 5), (33, 60, 20, 7, 3), (600, 96, 40, 6, 2)])
 def test_routed_experts_kernels(dtype, T, D, ff, experts, top):
     """Listing per expert, both grouped products and the weighted sum; widths that are no multiple of 8 take the
-    general kernel also in bfloat16.  One expert gets most tokens (more than one tile), another none."""
+    general kernel also in bfloat16.  One expert gets most tokens (more than one tile), another none.  The last
+    case has enough rows for the library's grouped product in bfloat16."""
     from pico_vllm_b200 import ops
     g = torch.Generator().manual_seed(T + D)
     h = torch.randn(T, D, generator=g).to(dtype)
@@ -389,6 +392,24 @@ def test_greedy_generation_through_the_entry_point(dtype, tmp_path):
     model = plain.PlainZapipel(raw, _tensors("p"), torch.float64)
     for p, o in zip(prompts, outs):
         assert list(o.token_ids) == model.greedy(p, 12)
+
+
+def test_command_line_writes_a_model_folder_and_generates(tmp_path, capsys):
+    from pico_vllm_b200.cli import main
+    (tmp_path / "config.json").write_text(json.dumps(SHAPES["m"]))
+    folder = str(tmp_path / "model")
+    assert main(["random-model", "--config", str(tmp_path / "config.json"), "--seed", "9", "--out", folder, "--std", str(STD)]) == 0
+    capsys.readouterr()
+    prompts = [[5, 17, 3], [9, 9]]
+    rc = main(["run", "--model", folder, "--dtype", "float32", "--prompt-ids", "5,17,3", "--prompt-ids", "9,9",
+               "--max-new-tokens", "5", "--temperature", "0", "--num-gpu-blocks", "32", "--ignore-eos"])
+    assert rc == 0
+    lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("[")]
+    printed = {int(l[1:l.index("]")]): [int(t) for t in l.split("] ")[1].split()] for l in lines}
+    from safetensors.torch import load_file
+    model = plain.PlainZapipel(SHAPES["m"], load_file(os.path.join(folder, "model.safetensors")), torch.float64)
+    for rid, p in enumerate(prompts):       # prompt and generated tokens are printed together
+        assert printed[rid] == p + model.greedy(p, 5)
 
 
 def test_trace_replay_of_a_model_folder(tmp_path):
