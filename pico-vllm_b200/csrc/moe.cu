@@ -8,7 +8,7 @@
 //
 // moe_route_kernel     one block per token: z, the choice and the weights            -> idx, wgt [T, top]
 // moe_group_kernel     one block: entries (token, j) counted and listed per expert   -> offsets [E+1], tile_start
-//                      [E+1] (64-row tiles per expert, running), perm [T*top] (place in expert order -> entry)
+//                      [E+1] (tiles of bm rows per expert, running), perm [T*top] (place in expert order -> entry)
 // moe_gemm_*_kernel    one block per (64-row tile of one expert's entries, 64 output features): bfloat16 on
 //                      mma.sync.m16n8k16 from cp.async double-buffered tiles, or any type on the CUDA cores
 //                      (float32 models; widths that are no multiple of 8).  Epilogue GATE_UP: silu(gate) * up
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
 }
 
 // One block.  n entries (token-major: entry = t * top + j).
-__global__ void moe_group_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ offsets,
+__global__ void moe_group_kernel(const int* __restrict__ idx, int n, int E, int bm, int* __restrict__ offsets,
                                  int* __restrict__ tile_start, int* __restrict__ perm, int* __restrict__ place) {
     pdl_launch_dependents();
     pdl_wait();
@@ -126,7 +126,7 @@ __global__ void moe_group_kernel(const int* __restrict__ idx, int n, int E, int*
             tile_start[e] = tiles;
             starts[e] = at;
             at += counts[e];
-            tiles += (counts[e] + MOE_BM - 1) / MOE_BM;
+            tiles += (counts[e] + bm - 1) / bm;
         }
         offsets[E] = at;
         tile_start[E] = tiles;
@@ -154,7 +154,10 @@ __device__ __forceinline__ float moe_silu(float g) { return g / (1.0f + expf(-g)
 
 // bfloat16 on tensor cores.  a: EPI GATE_UP: x [T, K] (row of entry p: perm[p] / top); EPI DOWN: act [n, K] in
 // expert order.  w: [E, NW, K] with NW = 2 * N (gate rows, then up rows) or N.  K a multiple of 8.
-template <int EPI>
+// BM = 64: four warps take 16 rows each over all 64 features, two stages.  BM = 16 (a handful of tokens: an expert's
+// list is short and the kernel is a stream of weights): the four warps split the 64 features, four stages, and the
+// smaller block leaves room for four blocks per SM - three times the bytes in flight.
+template <int EPI, int BM>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w,
                                                            const int* __restrict__ offsets,
                                                            const int* __restrict__ tile_start,
@@ -163,25 +166,26 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
-    __shared__ __align__(16) bf16 sa[2][MOE_BM][MOE_LD];
-    __shared__ __align__(16) bf16 sw[2][NB][MOE_BN][MOE_LD];
-    __shared__ int src_row[MOE_BM];
+    constexpr int WM = BM / 16, WN = 4 / WM, NT = MOE_BN / WN / 8, ST = BM == 64 ? 2 : 4;
+    __shared__ __align__(16) bf16 sa[ST][BM][MOE_LD];
+    __shared__ __align__(16) bf16 sw[ST][NB][MOE_BN][MOE_LD];
+    __shared__ int src_row[BM];
     const int tile = blockIdx.x;
     if (tile >= tile_start[E]) return;
     const int e = moe_find_expert(tile_start, E, tile);
-    const int p0 = offsets[e] + (tile - tile_start[e]) * MOE_BM;
-    const int nrows = min(MOE_BM, offsets[e + 1] - p0);
+    const int p0 = offsets[e] + (tile - tile_start[e]) * BM;
+    const int nrows = min(BM, offsets[e + 1] - p0);
     const int n0 = blockIdx.y * MOE_BN;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int r = tid; r < MOE_BM; r += 128)
+    const int row0 = (warp % WM) * 16, col0 = (warp / WM) * NT * 8;
+    for (int r = tid; r < BM; r += 128)
         src_row[r] = r < nrows ? (EPI == MOE_GATE_UP ? perm[p0 + r] / top : p0 + r) : -1;
     __syncthreads();
     const bf16* we = w + (size_t)e * NB * N * K;
 
     auto load = [&](int stage, int k0) {
-        // 64 rows x 4 chunks of 8 elements each for a, the same per weight block
-#pragma unroll
-        for (int c = tid; c < MOE_BM * 4; c += 128) {
+        // rows x 4 chunks of 8 elements each for a, the same per weight block
+        for (int c = tid; c < BM * 4; c += 128) {
             const int r = c >> 2, kc = (c & 3) * 8;
             const int sr = src_row[r];
             const bool ok = sr >= 0 && k0 + kc < K;
@@ -199,52 +203,52 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
         cp_async_commit();
     };
 
-    float acc[NB][MOE_BN / 8][4];
+    float acc[NB][NT][4];
 #pragma unroll
     for (int b = 0; b < NB; ++b)
 #pragma unroll
-        for (int j = 0; j < MOE_BN / 8; ++j)
+        for (int j = 0; j < NT; ++j)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[b][j][i] = 0.f;
 
     const int nk = (K + MOE_BK - 1) / MOE_BK;
-    load(0, 0);
+#pragma unroll
+    for (int s0 = 0; s0 < ST - 1; ++s0) {
+        if (s0 < nk) load(s0, s0 * MOE_BK);
+        else cp_async_commit();
+    }
     for (int kt = 0; kt < nk; ++kt) {
-        const int st = kt & 1;
-        if (kt + 1 < nk) {
-            load(st ^ 1, (kt + 1) * MOE_BK);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int st = kt % ST;
+        cp_async_wait<ST - 2>();         // the copies of stage kt have landed
+        __syncthreads();                 // ... for every thread, and everyone is done with stage kt - 1
+        if (kt + ST - 1 < nk) load((kt + ST - 1) % ST, (kt + ST - 1) * MOE_BK);
+        else cp_async_commit();
 #pragma unroll
         for (int kk = 0; kk < MOE_BK; kk += 16) {
             uint32_t fa[4];
-            ldmatrix_x4(fa, smem_u32(&sa[st][warp * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+            ldmatrix_x4(fa, smem_u32(&sa[st][row0 + (lane & 15)][kk + (lane >> 4) * 8]));
 #pragma unroll
             for (int b = 0; b < NB; ++b)
 #pragma unroll
-                for (int j = 0; j < MOE_BN / 8; j += 2) {
+                for (int j = 0; j < NT; j += 2) {
                     uint32_t fb[4];
-                    ldmatrix_x4(fb, smem_u32(&sw[st][b][j * 8 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]));
+                    ldmatrix_x4(fb, smem_u32(&sw[st][b][col0 + j * 8 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]));
                     mma_bf16(acc[b][j], fa, fb[0], fb[1]);
                     mma_bf16(acc[b][j + 1], fa, fb[2], fb[3]);
                 }
         }
-        __syncthreads();
     }
-    // epilogue: a thread holds rows warp*16 + lane/4 (+8) and columns j*8 + (lane%4)*2 (+1)
+    // epilogue: a thread holds rows row0 + lane/4 (+8) and columns col0 + j*8 + (lane%4)*2 (+1)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-        const int r = warp * 16 + (lane >> 2) + half * 8;
+        const int r = row0 + (lane >> 2) + half * 8;
         if (r >= nrows) continue;
         const int p = p0 + r;
 #pragma unroll
-        for (int j = 0; j < MOE_BN / 8; ++j) {
+        for (int j = 0; j < NT; ++j) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const int n = n0 + j * 8 + (lane & 3) * 2 + c;
+                const int n = n0 + col0 + j * 8 + (lane & 3) * 2 + c;
                 if (n >= N) continue;
                 if (EPI == MOE_GATE_UP) {
                     const float g = acc[0][j][half * 2 + c], u = acc[NB - 1][j][half * 2 + c];
@@ -377,15 +381,21 @@ PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int
     return pico_launch_status();
 }
 
-// The most 64-row tiles n entries over E experts can make.
-static inline int moe_max_tiles(int n, int E) { return n / MOE_BM + (n < E ? n : E); }
+// The most tiles of bm rows n entries over E experts can make.
+static inline int moe_max_tiles(int n, int E, int bm) { return n / bm + (n < E ? n : E); }
 
 // idx int32 [n]; offsets, tile_start int32 [E + 1]; perm int32 [n].
-PICO_API int pico_moe_group(const int* idx, int n, int E, int* offsets, int* tile_start, int* perm, int* place,
+// Rows per tile of the grouped products for n entries over E experts: 16 while the experts' lists are short.
+PICO_API int pico_moe_tile_rows(int n, int E, int dtype, int K1, int K2) {
+    const bool mma = dtype == PICO_BF16 && K1 % 8 == 0 && K2 % 8 == 0;
+    return mma && n <= 16 * E ? 16 : MOE_BM;
+}
+
+PICO_API int pico_moe_group(const int* idx, int n, int E, int bm, int* offsets, int* tile_start, int* perm, int* place,
                             cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (E < 1 || E > 4096) return PICO_ERR_SIZE;
-    pico_launch(moe_group_kernel, dim3(1), dim3(n >= 4096 ? 1024 : 256), (size_t)2 * E * sizeof(int), stream, idx, n, E,
+    if (E < 1 || E > 4096 || (bm != 16 && bm != MOE_BM)) return PICO_ERR_SIZE;
+    pico_launch(moe_group_kernel, dim3(1), dim3(n >= 4096 ? 1024 : 256), (size_t)2 * E * sizeof(int), stream, idx, n, E, bm,
                 offsets, tile_start, perm, place);
     return pico_launch_status();
 }
@@ -478,20 +488,24 @@ PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const flo
 }
 
 // epi 0: a = x [T, K], w [E, 2N, K] -> act [n, N];  epi 1: a = act [n, K], w [E, N, K] -> out2 float32 [n, N].
+// bm: the rows per tile that pico_moe_group was given (16 only for bfloat16 with K a multiple of 8).
 PICO_API int pico_moe_gemm(const void* a, const void* w, const int* offsets, const int* tile_start, const int* perm,
-                           int n, int E, int top, int N, int K, int epi, void* act, float* out2, int dtype,
+                           int n, int E, int top, int N, int K, int epi, int bm, void* act, float* out2, int dtype,
                            cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (N < 1 || K < 1 || (epi != MOE_GATE_UP && epi != MOE_DOWN)) return PICO_ERR_SIZE;
-    const dim3 grid(moe_max_tiles(n, E), (N + MOE_BN - 1) / MOE_BN);
+    if (N < 1 || K < 1 || (epi != MOE_GATE_UP && epi != MOE_DOWN) || (bm != 16 && bm != MOE_BM)) return PICO_ERR_SIZE;
+    if (bm == 16 && !(dtype == PICO_BF16 && K % 8 == 0)) return PICO_ERR_SIZE;
+    const dim3 grid(moe_max_tiles(n, E, bm), (N + MOE_BN - 1) / MOE_BN);
     if (grid.y > 65535) return PICO_ERR_SIZE;
+#define MOE_MMA(EPI_, BM_)                                                                                              \
+    pico_launch((moe_gemm_mma_kernel<EPI_, BM_>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets,  \
+                tile_start, perm, E, top, N, K, (bf16*)act, out2)
     if (dtype == PICO_BF16 && K % 8 == 0) {
-        if (epi == MOE_GATE_UP)
-            pico_launch((moe_gemm_mma_kernel<MOE_GATE_UP>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets,
-                        tile_start, perm, E, top, N, K, (bf16*)act, out2);
-        else
-            pico_launch((moe_gemm_mma_kernel<MOE_DOWN>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets,
-                        tile_start, perm, E, top, N, K, (bf16*)act, out2);
+        if (epi == MOE_GATE_UP) {
+            if (bm == 16) MOE_MMA(MOE_GATE_UP, 16); else MOE_MMA(MOE_GATE_UP, 64);
+        } else {
+            if (bm == 16) MOE_MMA(MOE_DOWN, 16); else MOE_MMA(MOE_DOWN, 64);
+        }
     } else if (dtype == PICO_BF16) {
         if (epi == MOE_GATE_UP)
             pico_launch((moe_gemm_simple_kernel<bf16, MOE_GATE_UP>), grid, dim3(256), 0, stream, (const bf16*)a, (const bf16*)w,

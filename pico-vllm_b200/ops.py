@@ -79,10 +79,11 @@ def library():
         "pico_latent_norm_store": [vp, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, vp, f32, i32, i32, vp],
         "pico_head_scale": [vp, vp, i32, i32, i32, i32, vp],
         "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp],
-        "pico_moe_group": [vp, i32, i32, vp, vp, vp, vp, vp],
+        "pico_moe_group": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
+        "pico_moe_tile_rows": [i32, i32, i32, i32, i32],
         "pico_moe_gather": [vp, vp, i32, i32, i32, vp, vp],
         "pico_moe_combine_placed": [vp, vp, vp, i32, i32, i32, vp, i32, vp],
-        "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
         "pico_moe_combine": [vp, vp, i32, i32, i32, vp, i32, vp],
     }
     for name, args in sigs.items():
@@ -862,7 +863,8 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
     meta = torch.empty(2 * (E + 1) + 2 * n, dtype=torch.int32, device=h.device)
     offsets, tile_start = meta[:E + 1], meta[E + 1:2 * (E + 1)]
     perm, place = meta[2 * (E + 1):2 * (E + 1) + n], meta[2 * (E + 1) + n:]
-    _check(lib.pico_moe_group(_ptr(idx), n, E, _ptr(offsets), _ptr(tile_start), _ptr(perm),
+    bm = lib.pico_moe_tile_rows(n, E, code, D, ff)      # rows per tile of this package's grouped kernels
+    _check(lib.pico_moe_group(_ptr(idx), n, E, bm, _ptr(offsets), _ptr(tile_start), _ptr(perm),
                               _ptr(place) if grouped else None, st), "moe_group")
     y = torch.empty((T, D), dtype=h.dtype, device=h.device)
     if grouped:
@@ -882,10 +884,10 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
         return y
     act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(h), _ptr(gate_up_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, ff, D,
-                             0, _ptr(act), None, code, st), "moe_gemm (gate_up)")
+                             0, bm, _ptr(act), None, code, st), "moe_gemm (gate_up)")
     out2 = torch.empty((n, D), dtype=torch.float32, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(act), _ptr(down_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, D, ff,
-                             1, None, _ptr(out2), code, st), "moe_gemm (down)")
+                             1, bm, None, _ptr(out2), code, st), "moe_gemm (down)")
     _check(lib.pico_moe_combine(_ptr(out2), _ptr(wgt), T, top, D, _ptr(y), code, st), "moe_combine")
     _count(4)
     return y
