@@ -105,7 +105,9 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
                         float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_list,
                         const int* __restrict__ tok_seg, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_stride, int nh, int nkv, int page_size,
-                        int window, float scale_log2, int n_splits, int cluster_reduce) {
+                        int window, float scale_log2, int n_splits, int cluster_reduce, int kv_same) {
+    // kv_same: keys and values are one tensor (a cached latent that serves as both): only the key tile is copied and
+    // the p.v product reads it too - the two maps give tiles of the same layout
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_dyn[];
     constexpr int TILE_BYTES = MMA_BN * HD * 2;                  // one K or V tile
@@ -183,10 +185,10 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
             int first = 0, last = ppt;
             while (first < last && n0 + (first + 1) * page_size <= lo) ++first;
             while (last > first && n0 + (last - 1) * page_size >= hi) --last;
-            if (lane == 0) mbar_expect_tx(full + s, (uint32_t)((last - first) * page_size * HD * 2 * 2));
+            if (lane == 0) mbar_expect_tx(full + s, (uint32_t)((last - first) * page_size * HD * 2 * (kv_same ? 1 : 2)));
             __syncwarp();
             const int pg = lane >> 1;
-            if (pg >= first && pg < last) {
+            if (pg >= first && pg < last && !(kv_same && (lane & 1))) {
                 const int e = it * ppt + pg;
                 const int page = e < TMA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
                 const int row = (page * nkv + kh) * page_size;
@@ -252,7 +254,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         }
         if (*abort_s) break;
         const uint32_t kt = smem_u32(tiles + (size_t)s * 2 * TILE_BYTES);
-        const uint32_t vt = kt + TILE_BYTES;
+        const uint32_t vt = kv_same ? kt : kt + TILE_BYTES;
         const int w0 = n0 + kw;
         if (w0 < hi && w0 + 16 > lo) {
             // q.k: four independent accumulators per head tile (a tensor-core instruction waits more
@@ -521,7 +523,7 @@ static bool tma_cluster_ok(int hd, int size, int nt, size_t smem) {
 PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const void* q, int q_row_stride, void* out,
                                    float* part_o, float* part_ml, const int* tok_list, int n_tok, const int* tok_seg,
                                    const int* positions, const int* block_table, int table_stride, int nh, int nkv,
-                                   int hd, int page_size, int window, float scale, int n_splits,
+                                   int hd, int page_size, int window, float scale, int n_splits, int kv_same,
                                    cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
@@ -553,7 +555,7 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
         pico_launch_cluster((paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT>), grid, dim3(5 * 32), smem, stream,    \
                             cluster ? n_splits : 1, km, vm, (const bf16*)q, q_row_stride, (bf16*)out, part_o,           \
                             part_ml, tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, page_size,       \
-                            window, scale_log2, n_splits, cluster);                                                     \
+                            window, scale_log2, n_splits, cluster, kv_same);                                            \
     } while (0)
     if (hd == 64) {
         if (nt == 1) LAUNCH_TMA(64, 1); else LAUNCH_TMA(64, 2);

@@ -19,8 +19,6 @@
 
 #define MOE_BM 64
 #define MOE_BN 64
-#define MOE_BK 32
-#define MOE_LD (MOE_BK + 8)      // bf16 elements per shared-memory row: 80 bytes, ldmatrix rows fall in distinct banks
 
 enum { MOE_GATE_UP = 0, MOE_DOWN = 1 };
 
@@ -156,8 +154,9 @@ __device__ __forceinline__ float moe_silu(float g) { return g / (1.0f + expf(-g)
 // expert order.  w: [E, NW, K] with NW = 2 * N (gate rows, then up rows) or N.  K a multiple of 8.
 // BM = 64: four warps take 16 rows each over all 64 features, two stages.  BM = 16 (a handful of tokens: an expert's
 // list is short and the kernel is a stream of weights): the four warps split the 64 features, four stages, and the
-// smaller block leaves room for four blocks per SM - three times the bytes in flight.
-template <int EPI, int BM>
+// smaller block leaves room for four blocks per SM - three times the bytes in flight; the down product, whose blocks
+// are few (width / 64 per expert) and hold one weight block a stage, takes 64 instead of 32 of K per stage.
+template <int EPI, int BM, int BK>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w,
                                                            const int* __restrict__ offsets,
                                                            const int* __restrict__ tile_start,
@@ -167,8 +166,9 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
     pdl_wait();
     constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
     constexpr int WM = BM / 16, WN = 4 / WM, NT = MOE_BN / WN / 8, ST = BM == 64 ? 2 : 4;
-    __shared__ __align__(16) bf16 sa[ST][BM][MOE_LD];
-    __shared__ __align__(16) bf16 sw[ST][NB][MOE_BN][MOE_LD];
+    constexpr int LD = BK + 8, CH = BK / 8;      // elements per shared-memory row (ldmatrix rows in distinct banks); 16-byte chunks per row
+    __shared__ __align__(16) bf16 sa[ST][BM][LD];
+    __shared__ __align__(16) bf16 sw[ST][NB][MOE_BN][LD];
     __shared__ int src_row[BM];
     const int tile = blockIdx.x;
     if (tile >= tile_start[E]) return;
@@ -184,9 +184,9 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
     const bf16* we = w + (size_t)e * NB * N * K;
 
     auto load = [&](int stage, int k0) {
-        // rows x 4 chunks of 8 elements each for a, the same per weight block
-        for (int c = tid; c < BM * 4; c += 128) {
-            const int r = c >> 2, kc = (c & 3) * 8;
+        // rows x CH chunks of 8 elements each for a, the same per weight block
+        for (int c = tid; c < BM * CH; c += 128) {
+            const int r = c / CH, kc = (c % CH) * 8;
             const int sr = src_row[r];
             const bool ok = sr >= 0 && k0 + kc < K;
             cp_async_16(smem_u32(&sa[stage][r][kc]), a + (size_t)(ok ? sr : 0) * K + (ok ? k0 + kc : 0), ok);
@@ -194,8 +194,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
 #pragma unroll
         for (int b = 0; b < NB; ++b)
 #pragma unroll
-            for (int c = tid; c < MOE_BN * 4; c += 128) {
-                const int r = c >> 2, kc = (c & 3) * 8;
+            for (int c = tid; c < MOE_BN * CH; c += 128) {
+                const int r = c / CH, kc = (c % CH) * 8;
                 const bool ok = n0 + r < N && k0 + kc < K;
                 cp_async_16(smem_u32(&sw[stage][b][r][kc]),
                             we + ((size_t)b * N + (ok ? n0 + r : 0)) * K + (ok ? k0 + kc : 0), ok);
@@ -211,20 +211,20 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[b][j][i] = 0.f;
 
-    const int nk = (K + MOE_BK - 1) / MOE_BK;
+    const int nk = (K + BK - 1) / BK;
 #pragma unroll
     for (int s0 = 0; s0 < ST - 1; ++s0) {
-        if (s0 < nk) load(s0, s0 * MOE_BK);
+        if (s0 < nk) load(s0, s0 * BK);
         else cp_async_commit();
     }
     for (int kt = 0; kt < nk; ++kt) {
         const int st = kt % ST;
         cp_async_wait<ST - 2>();         // the copies of stage kt have landed
         __syncthreads();                 // ... for every thread, and everyone is done with stage kt - 1
-        if (kt + ST - 1 < nk) load((kt + ST - 1) % ST, (kt + ST - 1) * MOE_BK);
+        if (kt + ST - 1 < nk) load((kt + ST - 1) % ST, (kt + ST - 1) * BK);
         else cp_async_commit();
 #pragma unroll
-        for (int kk = 0; kk < MOE_BK; kk += 16) {
+        for (int kk = 0; kk < BK; kk += 16) {
             uint32_t fa[4];
             ldmatrix_x4(fa, smem_u32(&sa[st][row0 + (lane & 15)][kk + (lane >> 4) * 8]));
 #pragma unroll
@@ -497,14 +497,14 @@ PICO_API int pico_moe_gemm(const void* a, const void* w, const int* offsets, con
     if (bm == 16 && !(dtype == PICO_BF16 && K % 8 == 0)) return PICO_ERR_SIZE;
     const dim3 grid(moe_max_tiles(n, E, bm), (N + MOE_BN - 1) / MOE_BN);
     if (grid.y > 65535) return PICO_ERR_SIZE;
-#define MOE_MMA(EPI_, BM_)                                                                                              \
-    pico_launch((moe_gemm_mma_kernel<EPI_, BM_>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets,  \
+#define MOE_MMA(EPI_, BM_, BK_)                                                                                             \
+    pico_launch((moe_gemm_mma_kernel<EPI_, BM_, BK_>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets, \
                 tile_start, perm, E, top, N, K, (bf16*)act, out2)
     if (dtype == PICO_BF16 && K % 8 == 0) {
         if (epi == MOE_GATE_UP) {
-            if (bm == 16) MOE_MMA(MOE_GATE_UP, 16); else MOE_MMA(MOE_GATE_UP, 64);
+            if (bm == 16) MOE_MMA(MOE_GATE_UP, 16, 32); else MOE_MMA(MOE_GATE_UP, 64, 32);
         } else {
-            if (bm == 16) MOE_MMA(MOE_DOWN, 16); else MOE_MMA(MOE_DOWN, 64);
+            if (bm == 16) MOE_MMA(MOE_DOWN, 16, 64); else MOE_MMA(MOE_DOWN, 64, 32);
         }
     } else if (dtype == PICO_BF16) {
         if (epi == MOE_GATE_UP)

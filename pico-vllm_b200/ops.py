@@ -65,7 +65,7 @@ def library():
                                        vp],
         "pico_make_kv_tensor_map": [vp, vp, i64, i32, i32],
         "pico_paged_decode_tma": [vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
-                                  f32, i32, vp],
+                                  f32, i32, i32, vp],
         "pico_tma_status": [vp],
         "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32, i32],
         "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32,
@@ -423,7 +423,8 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
             _check(lib.pico_paged_decode_tma(k_map[1], v_map[1], _ptr(q), q.stride(0), _ptr(out), part_o, part_ml,
                                              _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg), _ptr(positions),
                                              _ptr(block_table), block_table.stride(0), n_heads, n_kv_heads,
-                                             head_dim, page_size, win, float(scale), n_splits, _stream()),
+                                             head_dim, page_size, win, float(scale), n_splits,
+                                             1 if k_pages.data_ptr() == v_pages.data_ptr() else 0, _stream()),
                    f"paged_decode_tma (head_dim {head_dim})")
         else:
             _check(lib.pico_paged_decode_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o,
