@@ -59,11 +59,18 @@ SHAPES = {
               layers=[_layer(_mixer(20, 16, 16, 64, 128, 0.4), _moe(40, 9, 4)),
                       _layer(_mixer(8, 32, 64, 32, 128, 0.25, kv_from=0), dict(kind="dense", ff=96)),
                       _layer(_mixer(1, 64, 48, 16, 16, 0.5), _moe(24, 3, 3))]),
+    # awkward sizes: a width that is a multiple of 4 only, an odd vocabulary, ranks and head sizes that are no
+    # multiples of 16 (a latent of 24 in a row of 32), a latent of 256, 3 of 7 experts of an inner size that is no
+    # multiple of 8
+    "r": dict(architecture="Zapipel", vocab=203, width=100, norm=dict(eps=1e-5), logit_scale=0.5, logit_softcap=20.0,
+              layers=[_layer(_mixer(5, 24, 40, 20, 24, 0.3), _moe(28, 7, 3)),
+                      _layer(_mixer(3, 8, 8, 36, 256, 0.2), dict(kind="dense", ff=52)),
+                      _layer(_mixer(2, 40, 24, 12, 24, 0.4, kv_from=0), dict(kind="dense", ff=104))]),
     # one layer, mixer only: the mixer alone between its norms
     "m": dict(architecture="Zapipel", vocab=257, width=96, norm=dict(eps=1e-5), logit_scale=0.8,
               layers=[_layer(_mixer(6, 32, 48, 40, 64, 1.0), None)]),
 }
-SEEDS = {"p": 11, "q": 22, "m": 33}
+SEEDS = {"p": 11, "q": 22, "m": 33, "r": 44}
 STD = 0.12      # weights large enough that attention and routers are far from uniform
 
 
@@ -119,11 +126,11 @@ def _compare(steps, reqs, got, logits, margins, dtype, what):
 
 _CUTS = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_tail_decode(r, 32),
          "portions": helpers.trace_portions, "mixed": lambda r: helpers.trace_mixed(r, max_live=4, seed=3)}
-LENGTHS = {"p": [1, 9, 33, 70, 150, 260], "q": [2, 17, 48, 97, 140], "m": [5, 31, 64, 65, 200]}
+LENGTHS = {"p": [1, 9, 33, 70, 150, 260], "q": [2, 17, 48, 97, 140], "m": [5, 31, 64, 65, 200], "r": [3, 40, 129, 75]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["p", "q", "m"])
+@pytest.mark.parametrize("name", ["p", "q", "m", "r"])
 @pytest.mark.parametrize("cut,graph", [("whole", False), ("tail", False), ("tail", True), ("portions", False),
                                        ("mixed", False), ("mixed", True)])
 def test_every_cutting_matches_plain(dtype, name, cut, graph):
