@@ -56,14 +56,16 @@ def model_from_tensors(config, tensors, cfg: EngineConfig):
     return model
 
 
-def max_model_len(model, cfg: EngineConfig) -> int:
+def max_model_len(model, cfg: EngineConfig) -> Optional[int]:
+    """The longest request: the engine's setting, else the model's own limit (``max_position_embeddings``), else
+    None - a model that encodes no positions has no limit of its own, and the cache decides."""
     limit = getattr(model.config, "max_position_embeddings", None)
     if cfg.max_model_len is not None:
         if limit is not None and cfg.max_model_len > limit:
             raise ConfigError(f"max_model_len {cfg.max_model_len} exceeds the model's "
                               f"max_position_embeddings {limit}")
         return cfg.max_model_len
-    return limit if limit is not None else 4096
+    return limit
 
 
 def make_cache(model, cfg: EngineConfig, poison_freed: bool = False) -> CacheManager:
@@ -84,10 +86,12 @@ def make_cache(model, cfg: EngineConfig, poison_freed: bool = False) -> CacheMan
         else:
             budget = 256 << 20
         pages = max(1, budget // per_page)
+        if longest is None:
+            longest = 4096          # nothing says how long a request may get: the reference's max_seq_len
         # no more than every request at full length needs
         pages = min(pages, cfg.max_num_seqs * -(-longest // cfg.page_size))
     if cfg.max_cache_tokens is not None or cfg.num_pages is not None:
-        longest = min(longest, pages * cfg.page_size)
+        longest = pages * cfg.page_size if longest is None else min(longest, pages * cfg.page_size)
     if pages < 1:
         raise OutOfPages("the cache would have no page")
     return CacheManager(model.cache_entries, cfg.page_size, pages, cfg.max_num_seqs, longest, dtype,

@@ -111,3 +111,14 @@ def test_random_model_folder(tmp_path):
     assert ff.gate_up_weight.shape == (4, 48, 48) and ff.down_weight.shape == (4, 48, 24)
     assert ff.router_weight.dtype == torch.float32 and ff.router_bias.dtype == torch.float32
     assert model.blocks[0].norm1.weight.dtype == torch.float32
+
+
+def test_a_model_without_positions_is_as_long_as_its_cache():
+    """Nothing in this design limits a request's length; the pool the engine is given does."""
+    from pico_vllm_b200.config import EngineConfig
+    from pico_vllm_b200.engine.core import make_cache, max_model_len
+    model = build_model(config_from_dict(RAW))
+    cfg = EngineConfig(dtype="float32", page_size=16, max_cache_tokens=8192, device="cpu")
+    assert max_model_len(model, cfg) is None
+    assert make_cache(model, cfg).max_seq_len == 8192
+    assert make_cache(model, EngineConfig(dtype="float32", max_cache_tokens=8192, max_model_len=100, device="cpu")).max_seq_len == 100

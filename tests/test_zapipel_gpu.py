@@ -251,6 +251,21 @@ def test_long_decoding_and_reused_slots(dtype):
     assert runner.graph_replays > 500
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_request_longer_than_any_default(dtype):
+    """5,000 tokens (nothing in this design limits a request's length but the pool): most of it as one prompt, then
+    portions and single tokens; the wanted places lie at the end and at page borders far back."""
+    raw, tensors = SHAPES["m"], _tensors("m", dtype=dtype)
+    ids = helpers.random_ids(5000, raw["vocab"], 91)
+    reqs = {"long": ids}
+    steps = [dict(entries=[dict(id="long", tokens=ids[:4700], want=[0, 15, 16, 4095, 4096, 4699])], end=[]),
+             dict(entries=[dict(id="long", tokens=ids[4700:4990], want=[0, 289])], end=[])]
+    steps += [dict(entries=[dict(id="long", tokens=[ids[i]], want=[0])], end=["long"] if i == 4999 else []) for i in range(4990, 5000)]
+    runner = _runner(raw, tensors, dtype, helpers.live_token_peak(steps), graph=True)
+    logits, margins = _oracle(raw, tensors, reqs)
+    _compare(steps, reqs, helpers.replay(runner, steps), logits, margins, dtype, f"long request/{dtype}")
+
+
 # ------------------------------------------------------------------ kernels alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width", [96, 130, 1000, 1536, 2048, 2304])
