@@ -400,6 +400,31 @@ def test_scale_and_soft_cap_kernel():
     assert float(padded[:, 33:].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_greedy_tokens_chosen_inside_the_head(graph):
+    """With a positive scale, scale and cap keep the order of the logits, so ``step(..., greedy=True)`` may choose the
+    tokens in the head's product kernel (bfloat16, a vocabulary that is a multiple of 16) without ever applying them:
+    the same steps through a second runner with logits give the same tokens."""
+    from pico_vllm_b200.engine import StepItem
+    raw = json.loads(json.dumps(SHAPES["p"]))
+    raw["vocab"] = 304
+    tensors = _tensors("p", raw, dtype="bfloat16")
+    ra = _runner(raw, tensors, "bfloat16", 512, graph=graph)
+    rb = _runner(raw, tensors, "bfloat16", 512, graph=graph)
+    prompts = [helpers.random_ids(n, raw["vocab"], 700 + n) for n in (9, 30, 4)]
+    sa, sb = [ra.cache.acquire(i) for i in range(3)], [rb.cache.acquire(i) for i in range(3)]
+    items = lambda slots, toks, want: [StepItem(s, t, w) for s, t, w in zip(slots, toks, want)]
+    want = [(len(p) - 1,) for p in prompts]
+    assert ra.step(items(sa, prompts, want), greedy=True) is None
+    last = rb.step(items(sb, prompts, want)).argmax(-1).tolist()
+    assert ra.feedback[:3].tolist() == last
+    for k in range(5):
+        toks = [[t] for t in last]
+        assert ra.step(items(sa, toks, [(0,)] * 3), greedy=True) is None
+        last = rb.step(items(sb, toks, [(0,)] * 3)).argmax(-1).tolist()
+        assert ra.feedback[:3].tolist() == last, f"decode step {k}"
+
+
 # ------------------------------------------------------------------ through the entry points
 @pytest.mark.parametrize("dtype", ["float32"])
 def test_greedy_generation_through_the_entry_point(dtype, tmp_path):
