@@ -790,10 +790,12 @@ def latent_norm_store(proj: torch.Tensor, q_off: int, q_rank: int, q_weight: tor
     return cq, gate
 
 
-def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """Per-head product: out[t, a, :] = x[t, a, :] @ weight[a] for x [T, H * K], weight [H, K, N], out [T, H * N]
-    (a strided batched library product over the heads, written straight into ``out``'s layout)."""
-    _cuda(x, weight, out)
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head product: out[t, a, :] = gate[t, a] * (x[t, a, :] @ weight[a]) for x [T, H * K], weight [H, K, N], out
+    [T, H * N]; ``gate`` float32 [T, H] or None: a strided batched library product over the heads, written straight
+    into ``out``'s layout, and the gate kernel.  (A kernel of this package's own for up to 16 tokens, a thread per
+    output feature with the gate in its epilogue, took 25 to 60 us a launch against 4 + 4 + 3 us and was dropped.)"""
+    _cuda(x, weight, out, gate)
     T = x.shape[0]
     H, K, N = weight.shape
     if x.shape != (T, H * K) or out.shape != (T, H * N) or not (x.is_contiguous() and out.is_contiguous()
@@ -801,7 +803,11 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> tor
         raise KernelError("head_linear: x [T, H K], weight [H, K, N] and out [T, H N] must be contiguous")
     if not (x.dtype == weight.dtype == out.dtype):
         raise KernelError("head_linear: x, weight and out must share one dtype")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (T, H) or not gate.is_contiguous()):
+        raise KernelError("head_linear: gate must be contiguous float32 [T, H]")
     torch.bmm(x.view(T, H, K).transpose(0, 1), weight, out=out.view(T, H, N).transpose(0, 1))
+    if gate is not None:
+        head_scale(out, gate, H)
     return out
 
 

@@ -127,6 +127,5 @@ class LatentAttention(Part):
             ops.paged_attention(qa, latent, latent, oa, batch.tok_seg, batch.positions, gb.block_table, H, 1, R,
                                 cache.page_size, self.window, self.scale, splits, batch.scratch)
         o = torch.empty((T, H * self.vdim), dtype=h.dtype, device=h.device)
-        ops.head_linear(oa, self.uv_weight, o)                  # o_a = W_uv[a] o'_a
-        ops.head_scale(o, gate, H)
+        ops.head_linear(oa, self.uv_weight, o, gate)            # o_a = gate_a * W_uv[a] o'_a
         return _linear(o, self.o_weight)

@@ -333,6 +333,24 @@ def test_latent_norm_store_kernel(dtype):
     assert float((gate2.cpu().double() - torch.sigmoid(p[:, q_rank:q_rank + heads])).abs().max()) < 1e-6
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,K,N", [(1, 3, 16, 48), (7, 5, 24, 200), (16, 2, 130, 9), (17, 4, 32, 64), (300, 6, 48, 40)])
+def test_per_head_products(dtype, T, H, K, N):
+    """out[t, a] = gate[t, a] * x[t, a] @ w[a], written in the [T, H N] layout."""
+    from pico_vllm_b200 import ops
+    g = torch.Generator().manual_seed(T * H + K)
+    x = torch.randn(T, H * K, generator=g).to(dtype)
+    w = (torch.randn(H, K, N, generator=g) * 0.3).to(dtype)
+    gate = torch.rand(T, H, generator=g)
+    want = torch.einsum("tak,akn->tan", x.double().view(T, H, K), w.double())
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for gt in (None, gate):
+        out = torch.empty(T, H * N, dtype=dtype, device=DEV)
+        ops.head_linear(x.to(DEV), w.to(DEV), out, None if gt is None else gt.to(DEV))
+        ref = want if gt is None else want * gt.double()[:, :, None]
+        assert float((out.cpu().double().view(T, H, N) - ref).abs().max()) < tol * float(ref.abs().max())
+
+
 @pytest.mark.parametrize("experts,top", [(5, 1), (12, 3), (40, 8), (3, 3)])
 @pytest.mark.parametrize("T,D", [(50, 72), (701, 72), (9, 70), (600, 50)])
 def test_router_kernel(experts, top, T, D):
