@@ -208,7 +208,89 @@ def sample(logits, temperature, top_p, uniform, out):
     return out
 
 
-NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
+# ------------------------------------------------------------------ norm -> add -> norm, latent attention, routed experts
+def _norm(u, kind, w, eps):
+    if kind == 0:
+        return u
+    if kind == 2:
+        u = u - u.mean(-1, keepdim=True)
+    y = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps)
+    return y if w is None else y * w
+
+
+def post_add_norm(x, delta, post_weight, post_kind, post_eps, weight, kind, eps, out, rows=None):
+    d = None if delta is None else _norm(delta.float(), post_kind, post_weight, post_eps)
+    if rows is None:
+        if d is not None:
+            x.add_(d)
+        src = x
+    else:
+        src = x[rows.long()]
+        if d is not None:
+            src = src + d[rows.long()]
+    if out is not None:
+        out.copy_(_norm(src, kind, weight, eps).to(out.dtype))
+    return out
+
+
+def scale_softcap(logits, scale, cap):
+    logits.mul_(scale)
+    if cap:
+        logits.copy_(cap * torch.tanh(logits / cap))
+    return logits
+
+
+def latent_norm_store(proj, q_off, q_rank, q_weight, kv_off, kv_rank, kv_weight, slots, cache, g_off, heads, eps):
+    p = proj.float()
+    cq = _norm(p[:, q_off:q_off + q_rank], 1, q_weight, eps).to(proj.dtype)
+    if kv_rank > 0:
+        c = _norm(p[:, kv_off:kv_off + kv_rank], 1, kv_weight, eps).to(cache.dtype)
+        flat = cache.view(-1, cache.shape[-1])
+        for t, s in enumerate(slots.tolist()):
+            if s >= 0:
+                flat[s].zero_()
+                flat[s, :kv_rank] = c[t]
+    return cq, torch.sigmoid(p[:, g_off:g_off + heads])
+
+
+def head_linear(x, weight, out, gate=None):
+    T = x.shape[0]
+    H, K, N = weight.shape
+    y = torch.einsum("tak,akn->tan", x.float().view(T, H, K), weight.float())
+    if gate is not None:
+        y = y * gate[:, :, None]
+    out.copy_(y.reshape(T, H * N).to(out.dtype))
+    return out
+
+
+def head_scale(o, gate, heads):
+    T = o.shape[0]
+    o.copy_((o.float().view(T, heads, -1) * gate[:, :, None]).view(T, -1).to(o.dtype))
+    return o
+
+
+def moe_route(h, router_weight, router_bias, top):
+    z = h.float() @ router_weight.t()
+    if router_bias is not None:
+        z = z + router_bias
+    val, idx = torch.topk(z, top, dim=-1)
+    return idx.to(torch.int32), torch.softmax(val, dim=-1)
+
+
+def moe_experts(h, idx, wgt, gate_up_weight, down_weight):
+    ff = gate_up_weight.shape[1] // 2
+    y = torch.zeros(h.shape, dtype=torch.float32)
+    for t in range(h.shape[0]):
+        for j in range(idx.shape[1]):
+            e = int(idx[t, j])
+            gu = gate_up_weight[e].float() @ h[t].float()
+            g, u = gu[:ff], gu[ff:]
+            y[t] += wgt[t, j] * (down_weight[e].float() @ (g * torch.sigmoid(g) * u))
+    return y.to(h.dtype)
+
+
+NAMES = ["post_add_norm", "scale_softcap", "latent_norm_store", "head_linear", "head_scale", "moe_route", "moe_experts",
+         "embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
          "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "make_kv_tensor_map_2d", "tc_takes", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
          "linear", "logits_linear", "sample"]
