@@ -876,19 +876,22 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
     y = torch.empty((T, D), dtype=h.dtype, device=h.device)
     if grouped:
         # many tokens: rows in expert order, the library's grouped products (their group ends are read on the device),
-        # the activation kernel between them
-        xs = torch.empty((n, D), dtype=h.dtype, device=h.device)
-        _check(lib.pico_moe_gather(_ptr(h), _ptr(perm), n, top, D * h.element_size(), _ptr(xs), st), "moe_gather")
-        _count(2)
-        ends = offsets[1:]
-        gu = torch._grouped_mm(xs, gate_up_weight.transpose(1, 2), offs=ends)
-        act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
-        swiglu(gu, act)
-        ys = torch._grouped_mm(act, down_weight.transpose(1, 2), offs=ends)
-        _check(lib.pico_moe_combine_placed(_ptr(ys), _ptr(place), _ptr(wgt), T, top, D, _ptr(y), code, st),
-               "moe_combine_placed")
-        _count()
-        return y
+        # the activation kernel between them.  A shape the library refuses goes to this package's kernels below.
+        try:
+            xs = torch.empty((n, D), dtype=h.dtype, device=h.device)
+            _check(lib.pico_moe_gather(_ptr(h), _ptr(perm), n, top, D * h.element_size(), _ptr(xs), st), "moe_gather")
+            ends = offsets[1:]
+            gu = torch._grouped_mm(xs, gate_up_weight.transpose(1, 2), offs=ends)
+            act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
+            swiglu(gu, act)
+            ys = torch._grouped_mm(act, down_weight.transpose(1, 2), offs=ends)
+            _check(lib.pico_moe_combine_placed(_ptr(ys), _ptr(place), _ptr(wgt), T, top, D, _ptr(y), code, st),
+                   "moe_combine_placed")
+            _count(3)
+            return y
+        except (RuntimeError, NotImplementedError):
+            if torch.cuda.is_current_stream_capturing():
+                raise
     act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(h), _ptr(gate_up_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, ff, D,
                              0, bm, _ptr(act), None, code, st), "moe_gemm (gate_up)")

@@ -371,11 +371,13 @@ def test_router_kernel(experts, top, T, D):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,D,ff,experts,top", [(1, 64, 32, 4, 2), (150, 96, 40, 6, 2), (300, 72, 24, 3, 1),
-                                                (70, 100, 36, 5, 5), (33, 60, 20, 7, 3), (600, 96, 40, 6, 2)])
+                                                (70, 100, 36, 5, 5), (33, 60, 20, 7, 3), (600, 96, 40, 6, 2), (600, 64, 8, 4, 2),
+                                                (1100, 72, 24, 3, 1)])
 def test_routed_experts_kernels(dtype, T, D, ff, experts, top):
     """Listing per expert, both grouped products and the weighted sum; widths that are no multiple of 8 take the
     general kernel also in bfloat16.  One expert gets most tokens (more than one tile), another none.  The last
-    case has enough rows for the library's grouped product in bfloat16."""
+    cases have enough rows for the library's grouped product in bfloat16 (one with an inner size of 8, one with one expert
+    per token)."""
     from pico_vllm_b200 import ops
     g = torch.Generator().manual_seed(T + D)
     h = torch.randn(T, D, generator=g).to(dtype)
