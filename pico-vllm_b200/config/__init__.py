@@ -1,7 +1,8 @@
 from .base import KeyReader, read_config_json, architecture_name
 from .qwen2 import Qwen2Config
 from .zapipel import ZapipelConfig
+from .zikupel import ZikupelConfig
 from .engine import EngineConfig, canonical_dtype
 
-__all__ = ["KeyReader", "read_config_json", "architecture_name", "Qwen2Config", "ZapipelConfig", "EngineConfig",
+__all__ = ["KeyReader", "read_config_json", "architecture_name", "Qwen2Config", "ZapipelConfig", "ZikupelConfig", "EngineConfig",
            "canonical_dtype"]

@@ -57,7 +57,7 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q, int q_row_stride, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ tok_seg, const int* __restrict__ positions, const int* __restrict__ block_table,
-    int table_stride, int nh, int nkv, int hd, int page_size, int window, float scale, int n_splits) {
+    int table_stride, int nh, int nkv, int hd, int page_size, int window, float scale, int n_splits, float softcap) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float q_s[];  // [warps][hd]
@@ -97,6 +97,7 @@ __global__ void paged_attention_generic_kernel(
                 const int page = table[n / page_size];
                 row = (((long long)page * nkv + kh) * page_size + (n % page_size)) * hd;
                 s = dot_row<T>(qw, k_pages + row, hd);
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);     // scores are bounded by +-softcap before the softmax
             }
             const float m_new = fmaxf(m, warp_max(s));
             const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
@@ -174,7 +175,7 @@ PICO_API int pico_paged_attention_generic(const void* q, int q_row_stride, const
                                           const void* v_pages, void* out, float* part_o, float* part_ml,
                                           const int* tok_seg, const int* positions, const int* block_table,
                                           int table_stride, int T, int nh, int nkv, int hd, int page_size,
-                                          int window, float scale, int n_splits, int act_dtype,
+                                          int window, float scale, int n_splits, float softcap, int act_dtype,
                                           cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hd % 16 != 0 || hd < 16 || hd > 32 * ATT_MAX_DPL) return PICO_ERR_SIZE;
@@ -188,13 +189,13 @@ PICO_API int pico_paged_attention_generic(const void* q, int q_row_stride, const
         if ((q_row_stride % 4) != 0) return PICO_ERR_ALIGN;
         pico_launch((paged_attention_generic_kernel<float>), dim3(grid), dim3(warps * 32), smem, stream, 
             (const float*)q, q_row_stride, (const float*)k_pages, (const float*)v_pages, (float*)out, part_o,
-            part_ml, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits);
+            part_ml, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits, softcap);
         if (n_splits > 1)
             pico_launch((attention_combine_kernel<float>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (float*)out, hd, n_splits);
     } else if (act_dtype == PICO_BF16) {
         pico_launch((paged_attention_generic_kernel<bf16>), dim3(grid), dim3(warps * 32), smem, stream, 
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, part_o, part_ml,
-            tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits);
+            tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits, softcap);
         if (n_splits > 1)
             pico_launch((attention_combine_kernel<bf16>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (bf16*)out, hd, n_splits);
     } else
@@ -262,7 +263,7 @@ PICO_API int pico_paged_attention_noalloc(const void* q, int q_row_stride, const
     float* part_ml = part_o + (size_t)T * nh * n_splits * hd;
     const int rc = pico_paged_attention_generic(q, q_row_stride, k_pages, v_pages, out, part_o, part_ml, tok_seg,
                                                 positions, block_table, table_stride, T, nh, nkv, hd, page_size,
-                                                window, scale, n_splits, act_dtype, stream);
+                                                window, scale, n_splits, 0.f, act_dtype, stream);
     if (rc == PICO_ERR_SIZE) return noalloc_fail(rc, err, err_len, "a size the attention kernels do not take");
     if (rc == PICO_ERR_DTYPE) return noalloc_fail(rc, err, err_len, "act_dtype must be 0 (float32) or 1 (bfloat16)");
     if (rc == PICO_ERR_ALIGN) return noalloc_fail(rc, err, err_len, "q_row_stride must be a multiple of 4 for float32");

@@ -125,7 +125,7 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
                          const bf16* __restrict__ v_pages, bf16* __restrict__ out, const int* __restrict__ seg_list,
                          const int* __restrict__ cu_q, const int* __restrict__ positions,
                          const int* __restrict__ block_table, int table_stride, int nh, int nkv, int hd,
-                         int page_size, int window, float scale_log2) {
+                         int page_size, int window, float scale_log2, float cap_log2, float cap_2x) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -203,7 +203,7 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
                     const int n = n0 + j * 8 + (lane & 3) * 2 + (e & 1);
                     const int r = e >> 1;
                     const bool vis = n <= row_pos[r] && n >= row_lo[r];
-                    s[j][e] = vis ? s[j][e] * scale_log2 : -INFINITY;
+                    s[j][e] = vis ? pico_score_log2(s[j][e], scale_log2, cap_log2, cap_2x) : -INFINITY;
                 }
             }
             online_softmax<HD_MAX, MMA_BN / 8>(s, m, l, o);
@@ -235,7 +235,7 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                         float* __restrict__ part_ml, const int* __restrict__ tok_list,
                         const int* __restrict__ tok_seg, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_stride, int nh, int nkv, int hd,
-                        int page_size, int window, float scale_log2, int n_splits) {
+                        int page_size, int window, float scale_log2, int n_splits, float cap_log2, float cap_2x) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -305,7 +305,7 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int n = w0 + j * 8 + (lane & 3) * 2 + (e & 1);
-                    s[j][e] = n < end ? s[j][e] * scale_log2 : -INFINITY;
+                    s[j][e] = n < end ? pico_score_log2(s[j][e], scale_log2, cap_log2, cap_2x) : -INFINITY;
                 }
             online_softmax<HD_MAX, 2>(s, m, l, o);
             pv_tile<HD_MAX, 2>(o, s, v_s + (buf * MMA_BN + warp * 16) * ld, hd, ld, lane);
@@ -418,7 +418,7 @@ static size_t decode_smem(int hd) {
 PICO_API int pico_paged_prefill_mma(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                     void* out, const int* seg_list, int n_segs, const int* cu_q, int max_q_len,
                                     const int* positions, const int* block_table, int table_stride, int nh,
-                                    int nkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
+                                    int nkv, int hd, int page_size, int window, float scale, float softcap, cudaStream_t stream) {
     if (n_segs <= 0 || max_q_len <= 0) return 0;
     if (hd % 16 != 0 || hd < 16 || hd > 256 || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
@@ -428,12 +428,13 @@ PICO_API int pico_paged_prefill_mma(const void* q, int q_row_stride, const void*
     const dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_segs);
     const size_t smem = prefill_smem(hd);
     const float scale_log2 = scale * 1.4426950408889634f;
+    const float cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, cap_2x = softcap > 0.f ? 2.0f * scale / softcap : 0.f;
 #define LAUNCH_PREFILL(HD)                                                                                          \
     do {                                                                                                            \
         cudaFuncSetAttribute(paged_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         pico_launch((paged_prefill_mma_kernel<HD>), dim3(grid), dim3(MMA_THREADS), smem, stream,                                           \
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seg_list, cu_q,   \
-            positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2);                      \
+            positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2, cap_log2, cap_2x);    \
     } while (0)
     if (hd <= 64) LAUNCH_PREFILL(64);
     else if (hd <= 128) LAUNCH_PREFILL(128);
@@ -449,7 +450,7 @@ PICO_API int pico_paged_decode_mma(const void* q, int q_row_stride, const void* 
                                    void* out, float* part_o, float* part_ml, const int* tok_list, int n_tok,
                                    const int* tok_seg, const int* positions, const int* block_table,
                                    int table_stride, int nh, int nkv, int hd, int page_size, int window,
-                                   float scale, int n_splits, cudaStream_t stream) {
+                                   float scale, int n_splits, float softcap, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (hd % 16 != 0 || hd < 16 || hd > 256 || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
@@ -459,13 +460,14 @@ PICO_API int pico_paged_decode_mma(const void* q, int q_row_stride, const void* 
     const dim3 grid(n_splits, nkv, n_tok);
     const size_t smem = decode_smem(hd);
     const float scale_log2 = scale * 1.4426950408889634f;
+    const float cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, cap_2x = softcap > 0.f ? 2.0f * scale / softcap : 0.f;
 #define LAUNCH_DECODE(HD)                                                                                          \
     do {                                                                                                           \
         cudaFuncSetAttribute(paged_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         pico_launch((paged_decode_mma_kernel<HD>), dim3(grid), dim3(MMA_THREADS), smem, stream,                                           \
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, part_o, part_ml, \
             tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2,   \
-            n_splits);                                                                                             \
+            n_splits, cap_log2, cap_2x);                                                                           \
     } while (0)
     if (hd <= 64) LAUNCH_DECODE(64);
     else if (hd <= 128) LAUNCH_DECODE(128);

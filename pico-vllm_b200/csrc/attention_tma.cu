@@ -105,7 +105,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
                         float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_list,
                         const int* __restrict__ tok_seg, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_stride, int nh, int nkv, int page_size,
-                        int window, float scale_log2, int n_splits, int cluster_reduce, int kv_same) {
+                        int window, float scale_log2, int n_splits, int cluster_reduce, int kv_same, float cap_log2, float cap_2x) {
     // kv_same: keys and values are one tensor (a cached latent that serves as both): only the key tile is copied and
     // the p.v product reads it too - the two maps give tiles of the same layout
     pdl_launch_dependents();
@@ -281,7 +281,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float v = (sc[nt][0][e] + sc[nt][1][e]) + (sc[nt][2][e] + sc[nt][3][e]);
-                    x[e] = ((e < 2) ? vis_a : vis_b) ? v * scale_log2 : -INFINITY;
+                    x[e] = ((e < 2) ? vis_a : vis_b) ? pico_score_log2(v, scale_log2, cap_log2, cap_2x) : -INFINITY;
                 }
                 float p[4];
 #pragma unroll
@@ -524,7 +524,7 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
                                    float* part_o, float* part_ml, const int* tok_list, int n_tok, const int* tok_seg,
                                    const int* positions, const int* block_table, int table_stride, int nh, int nkv,
                                    int hd, int page_size, int window, float scale, int n_splits, int kv_same,
-                                   cudaStream_t stream) {
+                                   float softcap, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
@@ -533,6 +533,7 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
     if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
     const dim3 grid(n_splits, nkv, n_tok);
     const float scale_log2 = scale * 1.4426950408889634f;
+    const float cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, cap_2x = softcap > 0.f ? 2.0f * scale / softcap : 0.f;
     // (one block per SM with more stages or eight consumer warps was measured slower: it keeps the next
     // kernel's blocks, which prefetch under programmatic launch, off the SM)
     const int stages = TMA_STAGES_MANY;
@@ -555,7 +556,7 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
         pico_launch_cluster((paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT>), grid, dim3(5 * 32), smem, stream,    \
                             cluster ? n_splits : 1, km, vm, (const bf16*)q, q_row_stride, (bf16*)out, part_o,           \
                             part_ml, tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, page_size,       \
-                            window, scale_log2, n_splits, cluster, kv_same);                                            \
+                            window, scale_log2, n_splits, cluster, kv_same, cap_log2, cap_2x);                          \
     } while (0)
     if (hd == 64) {
         if (nt == 1) LAUNCH_TMA(64, 1); else LAUNCH_TMA(64, 2);

@@ -65,6 +65,14 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// An attention score in log2 units (the softmax uses exp2): raw * scale_log2, or, with a soft cap c on the scaled score,
+// c * tanh(raw * scale / c) in the same units.  cap_log2 = c * log2(e) (0: no cap); cap_2x = 2 * scale / c.
+// tanh(x) = 1 - 2 / (e^(2x) + 1): exact at both ends, absolute error ~1e-7 near 0.
+__device__ __forceinline__ float pico_score_log2(float raw, float scale_log2, float cap_log2, float cap_2x) {
+    if (cap_log2 > 0.f) return cap_log2 * (1.0f - __fdividef(2.0f, __expf(raw * cap_2x) + 1.0f));
+    return raw * scale_log2;
+}
+
 static inline int pico_launch_status() { return (int)cudaGetLastError(); }
 
 // Multiprocessors of the current device (asked once per device; grids are sized from it).

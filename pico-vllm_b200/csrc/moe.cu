@@ -5,6 +5,9 @@
 //   z = W_r h + b_r                                  (float32; h in the activation type)
 //   chosen = the `top` largest z (the lower index first among equals); weight_j = softmax over the chosen z
 //   y = sum_j weight_j * W_down[e_j] ( silu(W_gate[e_j] h) * (W_up[e_j] h) )
+// or, for experts without a gate whose weight acts on their input (score mode 1: weight_j = sigmoid(z_j), not renormalised):
+//   y = sum_j W_down[e_j] act( W_up[e_j] (weight_j h) ) = sum_j W_down[e_j] act( weight_j * (W_up[e_j] h) ),  act = relu^2 or silu
+// (epilogue UP_ACT: the weight multiplies the float32 result of the up product, which is the product of the weighted input).
 //
 // moe_route_kernel     one block per token: z, the choice and the weights            -> idx, wgt [T, top]
 // moe_group_kernel     one block: entries (token, j) counted and listed per expert   -> offsets [E+1], tile_start
@@ -20,14 +23,16 @@
 #define MOE_BM 64
 #define MOE_BN 64
 
-enum { MOE_GATE_UP = 0, MOE_DOWN = 1 };
+enum { MOE_GATE_UP = 0, MOE_DOWN = 1, MOE_UP_ACT = 2 };
+enum { MOE_ACT_SILU = 0, MOE_ACT_RELU2 = 1 };
+enum { MOE_SCORE_SOFTMAX_CHOSEN = 0, MOE_SCORE_SIGMOID = 1 };
 
 // TOK tokens per block (their rows of h in shared memory as float32, so that a warp reads an expert's router row once
 // for all of them); 8 warps take the experts in turn; warp w < TOK then chooses for token w.
 template <typename TA, int TOK>
 __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h, const float* __restrict__ wr,
                                                         const float* __restrict__ br, int T, int D, int E, int top,
-                                                        int* __restrict__ idx, float* __restrict__ wgt) {
+                                                        int mode, int* __restrict__ idx, float* __restrict__ wgt) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float rsm[];       // TOK rows of D floats (D rounded up to 4), then TOK x E logits
@@ -92,7 +97,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
         }
         if (be == 0x7fffffff) be = 0;           // only NaN or -inf left: keep indices legal
         if (j == 0) first = best;
-        const float p = expf(best - first);
+        const float p = mode == MOE_SCORE_SIGMOID ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         sum += p;
         if (lane == j) { mine = p; mine_e = be; }
         __syncwarp();
@@ -101,7 +106,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const TA* __restrict__ h
     }
     if (lane < top) {
         idx[(size_t)t * top + lane] = mine_e;
-        wgt[(size_t)t * top + lane] = mine / sum;
+        wgt[(size_t)t * top + lane] = mode == MOE_SCORE_SIGMOID ? mine : mine / sum;
     }
 }
 
@@ -149,6 +154,10 @@ __device__ __forceinline__ int moe_find_expert(const int* __restrict__ tile_star
 }
 
 __device__ __forceinline__ float moe_silu(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float moe_act(float u, int act) {
+    if (act == MOE_ACT_RELU2) { const float r = fmaxf(u, 0.f); return r * r; }
+    return moe_silu(u);
+}
 
 // bfloat16 on tensor cores.  a: EPI GATE_UP: x [T, K] (row of entry p: perm[p] / top); EPI DOWN: act [n, K] in
 // expert order.  w: [E, NW, K] with NW = 2 * N (gate rows, then up rows) or N.  K a multiple of 8.
@@ -161,7 +170,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
                                                            const int* __restrict__ offsets,
                                                            const int* __restrict__ tile_start,
                                                            const int* __restrict__ perm, int E, int top, int N, int K,
-                                                           bf16* __restrict__ act, float* __restrict__ out2) {
+                                                           bf16* __restrict__ act, float* __restrict__ out2,
+                                                           const float* __restrict__ wgt, int act_kind) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
@@ -179,7 +189,7 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row0 = (warp % WM) * 16, col0 = (warp / WM) * NT * 8;
     for (int r = tid; r < BM; r += 128)
-        src_row[r] = r < nrows ? (EPI == MOE_GATE_UP ? perm[p0 + r] / top : p0 + r) : -1;
+        src_row[r] = r < nrows ? (EPI != MOE_DOWN ? perm[p0 + r] / top : p0 + r) : -1;
     __syncthreads();
     const bf16* we = w + (size_t)e * NB * N * K;
 
@@ -244,6 +254,7 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
         const int r = row0 + (lane >> 2) + half * 8;
         if (r >= nrows) continue;
         const int p = p0 + r;
+        const float wrow = (EPI == MOE_UP_ACT && wgt) ? wgt[perm[p]] : 1.0f;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
 #pragma unroll
@@ -253,6 +264,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
                 if (EPI == MOE_GATE_UP) {
                     const float g = acc[0][j][half * 2 + c], u = acc[NB - 1][j][half * 2 + c];
                     act[(size_t)p * N + n] = __float2bfloat16_rn(moe_silu(g) * u);
+                } else if (EPI == MOE_UP_ACT) {
+                    act[(size_t)p * N + n] = __float2bfloat16_rn(moe_act(wrow * acc[0][j][half * 2 + c], act_kind));
                 } else {
                     out2[(size_t)perm[p] * N + n] = acc[0][j][half * 2 + c];
                 }
@@ -267,7 +280,8 @@ __global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restri
                                                               const int* __restrict__ offsets,
                                                               const int* __restrict__ tile_start,
                                                               const int* __restrict__ perm, int E, int top, int N, int K,
-                                                              TA* __restrict__ act, float* __restrict__ out2) {
+                                                              TA* __restrict__ act, float* __restrict__ out2,
+                                                              const float* __restrict__ wgt, int act_kind) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int NB = EPI == MOE_GATE_UP ? 2 : 1;
@@ -283,7 +297,7 @@ __global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restri
     const int n0 = blockIdx.y * MOE_BN;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     for (int r = tid; r < MOE_BM; r += 256)
-        src_row[r] = r < nrows ? (EPI == MOE_GATE_UP ? perm[p0 + r] / top : p0 + r) : -1;
+        src_row[r] = r < nrows ? (EPI != MOE_DOWN ? perm[p0 + r] / top : p0 + r) : -1;
     __syncthreads();
     const TA* we = w + (size_t)e * NB * N * K;
     float acc[NB][4][4];
@@ -329,12 +343,15 @@ __global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restri
         const int r = ty * 4 + i;
         if (r >= nrows) continue;
         const int p = p0 + r;
+        const float wrow = (EPI == MOE_UP_ACT && wgt) ? wgt[perm[p]] : 1.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             if (EPI == MOE_GATE_UP)
                 act[(size_t)p * N + n] = from_f32<TA>(moe_silu(acc[0][i][j]) * acc[NB - 1][i][j]);
+            else if (EPI == MOE_UP_ACT)
+                act[(size_t)p * N + n] = from_f32<TA>(moe_act(wrow * acc[0][i][j], act_kind));
             else
                 out2[(size_t)perm[p] * N + n] = acc[0][i][j];
         }
@@ -343,23 +360,23 @@ __global__ void __launch_bounds__(256) moe_gemm_simple_kernel(const TA* __restri
 
 template <typename TA>
 __global__ void moe_combine_kernel(const float* __restrict__ out2, const float* __restrict__ wgt, int top, int D,
-                                   size_t total, TA* __restrict__ y) {
+                                   size_t total, TA* __restrict__ y, const TA* __restrict__ base) {
     pdl_launch_dependents();
     pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / D;
         const int d = (int)(idx - t * D);
-        float acc = 0.f;
-        for (int j = 0; j < top; ++j) acc += wgt[t * top + j] * out2[(t * top + j) * (size_t)D + d];
+        float acc = base ? to_f32(base[idx]) : 0.f;        // wgt nullptr: a plain sum; base: added to it (a shared expert's output)
+        for (int j = 0; j < top; ++j) acc += (wgt ? wgt[t * top + j] : 1.0f) * out2[(t * top + j) * (size_t)D + d];
         y[idx] = from_f32<TA>(acc);
     }
 }
 
 // h [T, D]; wr float32 [E, D]; br float32 [E] or nullptr; idx int32 [T, top]; wgt float32 [T, top].
-PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int T, int D, int E, int top, int* idx,
-                            float* wgt, int dtype, cudaStream_t stream) {
+PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int T, int D, int E, int top, int mode,
+                            int* idx, float* wgt, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (E < 1 || top < 1 || top > E || top > 32 || E > 8192) return PICO_ERR_SIZE;
+    if (E < 1 || top < 1 || top > E || top > 32 || E > 8192 || mode < 0 || mode > 1) return PICO_ERR_SIZE;
     // four tokens a block when there are many (the router matrix is read once per block), one otherwise
     const int tok = T >= 512 ? 4 : 1;
     const size_t smem = ((size_t)tok * ((D + 3) & ~3) + (size_t)tok * E) * sizeof(float);
@@ -369,7 +386,7 @@ PICO_API int pico_moe_route(const void* h, const float* wr, const float* br, int
     do {                                                                                                                  \
         if (smem > 48 * 1024)                                                                                             \
             cudaFuncSetAttribute(moe_route_kernel<TA, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        pico_launch((moe_route_kernel<TA, TOK>), grid, dim3(256), smem, stream, (const TA*)h, wr, br, T, D, E, top, idx, wgt); \
+        pico_launch((moe_route_kernel<TA, TOK>), grid, dim3(256), smem, stream, (const TA*)h, wr, br, T, D, E, top, mode, idx, wgt); \
     } while (0)
     if (dtype == PICO_F32) {
         if (tok == 4) LAUNCH_ROUTE(float, 4); else LAUNCH_ROUTE(float, 1);
@@ -430,7 +447,8 @@ PICO_API int pico_moe_gather(const void* x, const int* perm, int n, int top, int
 // VEC: D a multiple of 8 (bfloat16) or 4 (float32): 16 bytes per access.
 template <typename TA, bool VEC>
 __global__ void moe_combine_placed_kernel(const TA* __restrict__ ys, const int* __restrict__ place,
-                                          const float* __restrict__ wgt, int top, int D, size_t total, TA* __restrict__ y) {
+                                          const float* __restrict__ wgt, int top, int D, size_t total, TA* __restrict__ y,
+                                          const TA* __restrict__ base) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int W = VEC ? 16 / (int)sizeof(TA) : 1;
@@ -440,9 +458,9 @@ __global__ void moe_combine_placed_kernel(const TA* __restrict__ ys, const int* 
         const int d = (int)(idx - t * Dv) * W;
         float acc[W];
 #pragma unroll
-        for (int k = 0; k < W; ++k) acc[k] = 0.f;
+        for (int k = 0; k < W; ++k) acc[k] = base ? to_f32(base[t * (size_t)D + d + k]) : 0.f;
         for (int j = 0; j < top; ++j) {
-            const float g = wgt[t * top + j];
+            const float g = wgt ? wgt[t * top + j] : 1.0f;
             const TA* row = ys + (size_t)place[t * top + j] * D + d;
             if (VEC) {
                 const uint4 raw = *reinterpret_cast<const uint4*>(row);
@@ -466,7 +484,7 @@ __global__ void moe_combine_placed_kernel(const TA* __restrict__ ys, const int* 
 }
 
 PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const float* wgt, int T, int top, int D, void* y,
-                                     int dtype, cudaStream_t stream) {
+                                     const void* base, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (dtype != PICO_F32 && dtype != PICO_BF16) return PICO_ERR_DTYPE;
     const int w = dtype == PICO_F32 ? 4 : 8;
@@ -477,7 +495,7 @@ PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const flo
     const int blocks = (int)((long long)want > cap ? cap : (long long)want);
 #define LAUNCH_CP(TA, V)                                                                                              \
     pico_launch((moe_combine_placed_kernel<TA, V>), dim3(blocks), dim3(256), 0, stream, (const TA*)ys, place, wgt, top, D, \
-                total, (TA*)y)
+                total, (TA*)y, (const TA*)base)
     if (dtype == PICO_F32) {
         if (vec) LAUNCH_CP(float, true); else LAUNCH_CP(float, false);
     } else {
@@ -490,53 +508,90 @@ PICO_API int pico_moe_combine_placed(const void* ys, const int* place, const flo
 // epi 0: a = x [T, K], w [E, 2N, K] -> act [n, N];  epi 1: a = act [n, K], w [E, N, K] -> out2 float32 [n, N].
 // bm: the rows per tile that pico_moe_group was given (16 only for bfloat16 with K a multiple of 8).
 PICO_API int pico_moe_gemm(const void* a, const void* w, const int* offsets, const int* tile_start, const int* perm,
-                           int n, int E, int top, int N, int K, int epi, int bm, void* act, float* out2, int dtype,
-                           cudaStream_t stream) {
+                           int n, int E, int top, int N, int K, int epi, int bm, void* act, float* out2,
+                           const float* wgt, int act_kind, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (N < 1 || K < 1 || (epi != MOE_GATE_UP && epi != MOE_DOWN) || (bm != 16 && bm != MOE_BM)) return PICO_ERR_SIZE;
+    if (N < 1 || K < 1 || epi < 0 || epi > 2 || act_kind < 0 || act_kind > 1 || (bm != 16 && bm != MOE_BM)) return PICO_ERR_SIZE;
     if (bm == 16 && !(dtype == PICO_BF16 && K % 8 == 0)) return PICO_ERR_SIZE;
     const dim3 grid(moe_max_tiles(n, E, bm), (N + MOE_BN - 1) / MOE_BN);
     if (grid.y > 65535) return PICO_ERR_SIZE;
 #define MOE_MMA(EPI_, BM_, BK_)                                                                                             \
     pico_launch((moe_gemm_mma_kernel<EPI_, BM_, BK_>), grid, dim3(128), 0, stream, (const bf16*)a, (const bf16*)w, offsets, \
-                tile_start, perm, E, top, N, K, (bf16*)act, out2)
+                tile_start, perm, E, top, N, K, (bf16*)act, out2, wgt, act_kind)
     if (dtype == PICO_BF16 && K % 8 == 0) {
         if (epi == MOE_GATE_UP) {
             if (bm == 16) MOE_MMA(MOE_GATE_UP, 16, 32); else MOE_MMA(MOE_GATE_UP, 64, 32);
+        } else if (epi == MOE_UP_ACT) {
+            if (bm == 16) MOE_MMA(MOE_UP_ACT, 16, 64); else MOE_MMA(MOE_UP_ACT, 64, 32);
         } else {
             if (bm == 16) MOE_MMA(MOE_DOWN, 16, 64); else MOE_MMA(MOE_DOWN, 64, 32);
         }
     } else if (dtype == PICO_BF16) {
-        if (epi == MOE_GATE_UP)
-            pico_launch((moe_gemm_simple_kernel<bf16, MOE_GATE_UP>), grid, dim3(256), 0, stream, (const bf16*)a, (const bf16*)w,
-                        offsets, tile_start, perm, E, top, N, K, (bf16*)act, out2);
-        else
-            pico_launch((moe_gemm_simple_kernel<bf16, MOE_DOWN>), grid, dim3(256), 0, stream, (const bf16*)a, (const bf16*)w,
-                        offsets, tile_start, perm, E, top, N, K, (bf16*)act, out2);
+#define MOE_SIMPLE(TA_, EPI_)                                                                                              \
+    pico_launch((moe_gemm_simple_kernel<TA_, EPI_>), grid, dim3(256), 0, stream, (const TA_*)a, (const TA_*)w, offsets,     \
+                tile_start, perm, E, top, N, K, (TA_*)act, out2, wgt, act_kind)
+        if (epi == MOE_GATE_UP) MOE_SIMPLE(bf16, MOE_GATE_UP);
+        else if (epi == MOE_UP_ACT) MOE_SIMPLE(bf16, MOE_UP_ACT);
+        else MOE_SIMPLE(bf16, MOE_DOWN);
     } else if (dtype == PICO_F32) {
-        if (epi == MOE_GATE_UP)
-            pico_launch((moe_gemm_simple_kernel<float, MOE_GATE_UP>), grid, dim3(256), 0, stream, (const float*)a,
-                        (const float*)w, offsets, tile_start, perm, E, top, N, K, (float*)act, out2);
-        else
-            pico_launch((moe_gemm_simple_kernel<float, MOE_DOWN>), grid, dim3(256), 0, stream, (const float*)a,
-                        (const float*)w, offsets, tile_start, perm, E, top, N, K, (float*)act, out2);
+        if (epi == MOE_GATE_UP) MOE_SIMPLE(float, MOE_GATE_UP);
+        else if (epi == MOE_UP_ACT) MOE_SIMPLE(float, MOE_UP_ACT);
+        else MOE_SIMPLE(float, MOE_DOWN);
+#undef MOE_SIMPLE
     } else
         return PICO_ERR_DTYPE;
     return pico_launch_status();
 }
 
 // out2 float32 [T * top, D]; wgt float32 [T, top]; y [T, D].
-PICO_API int pico_moe_combine(const float* out2, const float* wgt, int T, int top, int D, void* y, int dtype,
-                              cudaStream_t stream) {
+PICO_API int pico_moe_combine(const float* out2, const float* wgt, int T, int top, int D, void* y, const void* base,
+                              int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     const size_t total = (size_t)T * D;
     const long long cap = 16LL * pico_num_sms();
     const size_t want = (total + 255) / 256;
     const int blocks = (int)((long long)want > cap ? cap : (long long)want);
     if (dtype == PICO_F32)
-        pico_launch((moe_combine_kernel<float>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (float*)y);
+        pico_launch((moe_combine_kernel<float>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (float*)y,
+                    (const float*)base);
     else if (dtype == PICO_BF16)
-        pico_launch((moe_combine_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (bf16*)y);
+        pico_launch((moe_combine_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, out2, wgt, top, D, total, (bf16*)y,
+                    (const bf16*)base);
+    else
+        return PICO_ERR_DTYPE;
+    return pico_launch_status();
+}
+
+// out[p, :] = act(wgt[perm[p]] * u[p, :]) in float32: the activation of experts without a gate between the library's
+// two grouped products (rows in expert order), with the entry's router weight acting on the expert's input.  perm and
+// wgt nullptr: a plain activation over [n, ff] (a dense layer of the same form, such as a shared expert).  In place
+// when out == u.
+template <typename TA>
+__global__ void moe_scaled_act_kernel(const TA* u, const int* __restrict__ perm, const float* __restrict__ wgt, int ff,
+                                      size_t total, int act_kind, TA* out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = idx / ff;
+        const float w = wgt ? wgt[perm ? perm[p] : p] : 1.0f;
+        out[idx] = from_f32<TA>(moe_act(w * to_f32(u[idx]), act_kind));
+    }
+}
+
+PICO_API int pico_moe_scaled_act(const void* u, const int* perm, const float* wgt, int n, int ff, int act_kind, void* out,
+                                 int dtype, cudaStream_t stream) {
+    if (n <= 0 || ff <= 0) return 0;
+    if (act_kind < 0 || act_kind > 1) return PICO_ERR_SIZE;
+    const size_t total = (size_t)n * ff;
+    const long long cap = 16LL * pico_num_sms();
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)((long long)want > cap ? cap : (long long)want);
+    if (dtype == PICO_F32)
+        pico_launch((moe_scaled_act_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)u, perm, wgt, ff, total,
+                    act_kind, (float*)out);
+    else if (dtype == PICO_BF16)
+        pico_launch((moe_scaled_act_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, (const bf16*)u, perm, wgt, ff, total,
+                    act_kind, (bf16*)out);
     else
         return PICO_ERR_DTYPE;
     return pico_launch_status();

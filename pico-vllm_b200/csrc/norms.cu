@@ -11,7 +11,7 @@
 // All arithmetic in float32; d and y are in the activation type.
 #include "common.cuh"
 
-enum { NORM_NONE = 0, NORM_RMS = 1, NORM_CENTRED = 2 };
+enum { NORM_NONE = 0, NORM_RMS = 1, NORM_CENTRED = 2, NORM_COPY = 3 };   // COPY: no norm, but the row is written out in the activation type
 
 // Four elements of the activation type from / to memory in one access.
 template <typename TA> struct Row4;
@@ -132,7 +132,8 @@ __global__ void post_add_norm_kernel(float* __restrict__ x, const TA* __restrict
         }
     }
     if (!out || kind == NORM_NONE) return;
-    norm_row_inplace<VEC>(vals, H, kind, w, eps, scratch);
+    if (kind != NORM_COPY) norm_row_inplace<VEC>(vals, H, kind, w, eps, scratch);
+    else __syncthreads();
     TA* dst = out + (size_t)r * H;
 #pragma unroll 4
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(128) post_add_norm_warp_kernel(float* __restri
         if (delta && !rows && lane + 32 * k < n4) *reinterpret_cast<float4*>(x + src + 4 * (lane + 32 * k)) = a[k];
     }
     if (!norm_out) return;
-    norm_regs<VPL>(a, w, n4, lane, H, kind, eps);
+    if (kind != NORM_COPY) norm_regs<VPL>(a, w, n4, lane, H, kind, eps);
     TA* dst = out + (size_t)r * H;
 #pragma unroll
     for (int k = 0; k < VPL; ++k)
@@ -234,7 +235,7 @@ PICO_API int pico_post_add_norm(float* x, const void* delta, const float* post_w
                                 const float* w, int kind, float eps, void* out, const int* rows, int R, int H,
                                 int act_dtype, cudaStream_t stream) {
     if (R <= 0) return 0;
-    if (post_kind < 0 || post_kind > 2 || kind < 0 || kind > 2) return PICO_ERR_SIZE;
+    if (post_kind < 0 || post_kind > 2 || kind < 0 || kind > 3) return PICO_ERR_SIZE;
     if (act_dtype != PICO_F32 && act_dtype != PICO_BF16) return PICO_ERR_DTYPE;
     if (H % 4 == 0 && H <= 2048) {       // a warp per row, the row in registers
         const int vpl = (H / 4 + 31) / 32;

@@ -20,6 +20,7 @@ from .errors import KernelError
 
 _F32, _BF16 = 0, 1
 NORM_NONE, NORM_RMS, NORM_CENTRED = 0, 1, 2      # kinds of norm the row kernels have
+NORM_COPY = 3      # as the output kind: no norm, the (added-to) stream row written out in the activation type
 _lib = None
 launches = 0  # kernels of this package launched so far (graph replays add their captured count)
 
@@ -52,10 +53,10 @@ def library():
         "pico_swiglu": [vp, vp, i32, i32, i32, vp],
         "pico_rope_store": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
         "pico_paged_attention_generic": [vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
-                                         i32, i32, f32, i32, i32, vp],
-        "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
+                                         i32, i32, f32, i32, f32, i32, vp],
+        "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp],
         "pico_paged_decode_mma": [vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
-                                  f32, i32, vp],
+                                  f32, i32, f32, vp],
         "pico_skinny_linear": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp, vp],
         "pico_skinny_argmax": [vp, i32, vp, vp, i32, i32, i32, vp, f32, vp, vp],
         "pico_skinny_norm_fits": [i32, i32],
@@ -65,7 +66,7 @@ def library():
                                        vp],
         "pico_make_kv_tensor_map": [vp, vp, i64, i32, i32],
         "pico_paged_decode_tma": [vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
-                                  f32, i32, i32, vp],
+                                  f32, i32, i32, f32, vp],
         "pico_tma_status": [vp],
         "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32, i32],
         "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32,
@@ -78,13 +79,19 @@ def library():
         "pico_scale_softcap": [vp, i32, i32, i32, f32, f32, vp],
         "pico_latent_norm_store": [vp, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp, i32, i32, i32, vp, f32, i32, i32, vp],
         "pico_head_scale": [vp, vp, i32, i32, i32, i32, vp],
-        "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_route": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp],
         "pico_moe_group": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_moe_tile_rows": [i32, i32, i32, i32, i32],
         "pico_moe_gather": [vp, vp, i32, i32, i32, vp, vp],
-        "pico_moe_combine_placed": [vp, vp, vp, i32, i32, i32, vp, i32, vp],
-        "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp],
-        "pico_moe_combine": [vp, vp, i32, i32, i32, vp, i32, vp],
+        "pico_moe_combine_placed": [vp, vp, vp, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_gemm": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, i32, i32, vp],
+        "pico_moe_combine": [vp, vp, i32, i32, i32, vp, vp, i32, vp],
+        "pico_moe_scaled_act": [vp, vp, vp, i32, i32, i32, vp, i32, vp],
+        "pico_qk_norm_rope_store": [vp, i32, vp, vp, vp, f32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                    i32, vp],
+        "pico_sigmoid_gate": [vp, vp, i32, i32, i32, i32, vp],
+        "pico_decay_linear_attention": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+        "pico_gated_rms_norm": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -231,8 +238,10 @@ def attention_scratch_floats(T: int, n_heads: int, head_dim: int, n_splits: int)
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                     tok_seg: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                     n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-                    scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
+                    softcap: Optional[float] = None) -> torch.Tensor:
     """Causal attention of every token of the batch over its request's cache pages.
+    ``softcap`` c: the scaled score s becomes c * tanh(s / c) before the softmax.
 
     q: [T, >= n_heads*head_dim] rows (the qkv buffer, queries first); out [T, n_heads*head_dim];
     tok_seg int32 [T]: row of block_table for each token; positions int32 [T]; block_table int32
@@ -267,7 +276,7 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     _check(library().pico_paged_attention_generic(
         _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o, part_ml, _ptr(tok_seg),
         _ptr(positions), _ptr(block_table), block_table.stride(0), T, n_heads, n_kv_heads, head_dim, page_size,
-        int(window) if window else 0, float(scale), n_splits, _dtype_code(q), _stream()),
+        int(window) if window else 0, float(scale), n_splits, float(softcap) if softcap else 0.0, _dtype_code(q), _stream()),
         f"paged_attention (head_dim {head_dim})")
     _count(2 if n_splits > 1 else 1)
     return out
@@ -361,7 +370,8 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                         max_prefill_q: int, decode_tokens: Optional[torch.Tensor], n_decode_tokens: int,
                         n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
                         scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
-                        k_map=None, v_map=None, k_map2d=None, v_map2d=None, pair_min_keys: int = 0) -> torch.Tensor:
+                        k_map=None, v_map=None, k_map2d=None, v_map2d=None, pair_min_keys: int = 0,
+                        softcap: Optional[float] = None) -> torch.Tensor:
     """The same attention as :func:`paged_attention` for bfloat16 on tensor cores, in two launches:
     segments that bring two or more tokens (``prefill_segs`` int32 [n_prefill_segs], None = all
     segments; ``cu_q`` int32 [segments + 1]; ``max_prefill_q`` their longest) and single tokens
@@ -388,6 +398,9 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
             raise KernelError("paged_attention_mma: index tensors must be int32")
     lib = library()
     win = int(window) if window else 0
+    cap = float(softcap) if softcap else 0.0
+    if cap > 0.0:
+        k_map2d = v_map2d = None        # the tcgen05 prompt kernel has no soft cap: portions take the mma.sync kernel
     if n_prefill_segs > 0 and k_map2d is not None and v_map2d is not None:
         # pair_min_keys > 0 (and scratch for two partial results per (token, head)): every query tile gets two
         # blocks, which share it when it sees at least that many keys; the pairs' counters are zero between launches
@@ -408,7 +421,7 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
         _check(lib.pico_paged_prefill_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out),
                                           _ptr(prefill_segs), n_prefill_segs, _ptr(cu_q), max_prefill_q,
                                           _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
-                                          n_kv_heads, head_dim, page_size, win, float(scale), _stream()),
+                                          n_kv_heads, head_dim, page_size, win, float(scale), cap, _stream()),
                f"paged_prefill_mma (head_dim {head_dim})")
         _count()
     if n_decode_tokens > 0:
@@ -424,13 +437,13 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                                              _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg), _ptr(positions),
                                              _ptr(block_table), block_table.stride(0), n_heads, n_kv_heads,
                                              head_dim, page_size, win, float(scale), n_splits,
-                                             1 if k_pages.data_ptr() == v_pages.data_ptr() else 0, _stream()),
+                                             1 if k_pages.data_ptr() == v_pages.data_ptr() else 0, cap, _stream()),
                    f"paged_decode_tma (head_dim {head_dim})")
         else:
             _check(lib.pico_paged_decode_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o,
                                              part_ml, _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg),
                                              _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
-                                             n_kv_heads, head_dim, page_size, win, float(scale), n_splits,
+                                             n_kv_heads, head_dim, page_size, win, float(scale), n_splits, cap,
                                              _stream()),
                    f"paged_decode_mma (head_dim {head_dim})")
         clustered = k_map is not None and v_map is not None and n_splits in (2, 4, 8, 16)
@@ -726,7 +739,7 @@ def post_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], post_weight: O
     if x.dtype != torch.float32 or not x.is_contiguous():
         raise KernelError("post_add_norm: x must be contiguous float32 [T, H]")
     for w, k, what in ((post_weight, post_kind, "post_weight"), (weight, kind, "weight")):
-        if k not in (NORM_NONE, NORM_RMS, NORM_CENTRED):
+        if k not in (NORM_NONE, NORM_RMS, NORM_CENTRED) and not (k == NORM_COPY and what == "weight"):
             raise KernelError(f"post_add_norm: unknown kind of norm {k}")
         if w is not None and (w.dtype != torch.float32 or w.shape != (H,)):
             raise KernelError(f"post_add_norm: {what} must be float32 [H]")
@@ -826,8 +839,14 @@ def head_scale(o: torch.Tensor, gate: torch.Tensor, heads: int) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------
 # Routed experts.
-def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optional[torch.Tensor], top: int):
-    """Router logits z = h W^T + b in float32, the ``top`` largest per token and the softmax over those alone.
+MOE_SCORE_SOFTMAX_CHOSEN, MOE_SCORE_SIGMOID = 0, 1
+MOE_ACT_SILU, MOE_ACT_RELU2 = 0, 1
+
+
+def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optional[torch.Tensor], top: int,
+              scoring: int = MOE_SCORE_SOFTMAX_CHOSEN):
+    """Router logits z = h W^T + b in float32, the ``top`` largest per token and the softmax over those alone
+    (``scoring`` MOE_SCORE_SIGMOID: each chosen expert's weight is sigmoid(z) of its own logit, not renormalised).
     h [T, D]; router_weight float32 [E, D]; router_bias float32 [E] or None.  Returns (idx int32 [T, top],
     weights float32 [T, top])."""
     _cuda(h, router_weight, router_bias)
@@ -840,30 +859,43 @@ def moe_route(h: torch.Tensor, router_weight: torch.Tensor, router_bias: Optiona
         raise KernelError("moe_route: the router bias must be float32 [E]")
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=h.device)
-    _check(library().pico_moe_route(_ptr(h), _ptr(router_weight), _ptr(router_bias), T, D, E, top, _ptr(idx), _ptr(wgt),
+    _check(library().pico_moe_route(_ptr(h), _ptr(router_weight), _ptr(router_bias), T, D, E, top, int(scoring), _ptr(idx), _ptr(wgt),
                                     _dtype_code(h), _stream()), f"moe_route ({E} experts, top {top})")
     _count()
     return idx, wgt
 
 
 def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_weight: torch.Tensor,
-                down_weight: torch.Tensor) -> torch.Tensor:
-    """sum_j wgt[t, j] * down[e] (silu(gate[e] h_t) * (up[e] h_t)) with e = idx[t, j]: the (token, j) entries are
-    listed per expert on the device, the two products run as grouped products over those lists, and the weighted sum
-    is taken in float32.  gate_up_weight [E, 2 ff, D] (gate rows, then up rows), down_weight [E, D, ff], both in
-    h's type.  Returns [T, D] in h's type."""
-    _cuda(h, idx, wgt, gate_up_weight, down_weight)
+                down_weight: torch.Tensor, gated: bool = True, act: int = MOE_ACT_SILU, weight_on_input: bool = False,
+                base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The routed experts' sum.  With e = idx[t, j]:
+
+    gated, weight on the output (the default):  sum_j wgt[t, j] * down[e] (silu(gate[e] h_t) * (up[e] h_t)),
+    gate_up_weight [E, 2 ff, D] (gate rows, then up rows);
+    not gated:  sum_j down[e] act(up[e] (wgt[t, j] h_t)) with ``weight_on_input`` (the weight multiplies the float32
+    result of the up product, which is the product of the weighted input), or sum_j wgt[t, j] * down[e] act(up[e] h_t)
+    without; gate_up_weight is then the up matrices [E, ff, D]; ``act`` MOE_ACT_SILU or MOE_ACT_RELU2 (relu squared).
+
+    The (token, j) entries are listed per expert on the device, the two products run as grouped products over those
+    lists, and the sum is taken in float32; ``base`` [T, D] (a shared expert's output) is added in the same kernel.
+    down_weight [E, D, ff]; all in h's type.  Returns [T, D] in h's type."""
+    _cuda(h, idx, wgt, gate_up_weight, down_weight, base)
     T, D = h.shape
     top = idx.shape[1]
-    E, ff2, _ = gate_up_weight.shape
-    ff = ff2 // 2
+    E, ff_rows, _ = gate_up_weight.shape
+    ff = ff_rows // 2 if gated else ff_rows
     if not (h.is_contiguous() and gate_up_weight.is_contiguous() and down_weight.is_contiguous()) \
-            or gate_up_weight.shape != (E, 2 * ff, D) or down_weight.shape != (E, D, ff) \
+            or gate_up_weight.shape != (E, (2 if gated else 1) * ff, D) or down_weight.shape != (E, D, ff) \
             or not (h.dtype == gate_up_weight.dtype == down_weight.dtype):
-        raise KernelError("moe_experts: needs contiguous h [T, D], gate_up [E, 2 ff, D] and down [E, D, ff] of one type")
+        raise KernelError("moe_experts: needs contiguous h [T, D], gate_up [E, 2 ff, D] (or up [E, ff, D]) and down [E, D, ff] "
+                          "of one type")
     if idx.dtype != torch.int32 or wgt.dtype != torch.float32 or idx.shape != (T, top) or wgt.shape != (T, top) \
             or not (idx.is_contiguous() and wgt.is_contiguous()):
         raise KernelError("moe_experts: idx int32 [T, top] and wgt float32 [T, top]")
+    if gated and (act != MOE_ACT_SILU or weight_on_input):
+        raise KernelError("moe_experts: gated experts are built with silu and the weight on the output only")
+    if base is not None and (base.shape != (T, D) or base.dtype != h.dtype or not base.is_contiguous()):
+        raise KernelError("moe_experts: base must be contiguous [T, D] in h's type")
     n = T * top
     lib, code, st = library(), _dtype_code(h), _stream()
     grouped = moe_library_takes(h, n, D, ff)
@@ -874,6 +906,8 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
     _check(lib.pico_moe_group(_ptr(idx), n, E, bm, _ptr(offsets), _ptr(tile_start), _ptr(perm),
                               _ptr(place) if grouped else None, st), "moe_group")
     y = torch.empty((T, D), dtype=h.dtype, device=h.device)
+    in_w = wgt if (not gated and weight_on_input) else None         # the weight inside the activation ...
+    out_w = None if (not gated and weight_on_input) else wgt        # ... or on the expert's output
     if grouped:
         # many tokens: rows in expert order, the library's grouped products (their group ends are read on the device),
         # the activation kernel between them.  A shape the library refuses goes to this package's kernels below.
@@ -882,24 +916,140 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, gate_up_w
             _check(lib.pico_moe_gather(_ptr(h), _ptr(perm), n, top, D * h.element_size(), _ptr(xs), st), "moe_gather")
             ends = offsets[1:]
             gu = torch._grouped_mm(xs, gate_up_weight.transpose(1, 2), offs=ends)
-            act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
-            swiglu(gu, act)
-            ys = torch._grouped_mm(act, down_weight.transpose(1, 2), offs=ends)
-            _check(lib.pico_moe_combine_placed(_ptr(ys), _ptr(place), _ptr(wgt), T, top, D, _ptr(y), code, st),
+            if gated:
+                a = torch.empty((n, ff), dtype=h.dtype, device=h.device)
+                swiglu(gu, a)
+            else:
+                a = gu
+                _check(lib.pico_moe_scaled_act(_ptr(gu), _ptr(perm), _ptr(in_w), n, ff, int(act), _ptr(a), code, st),
+                       "moe_scaled_act")
+            ys = torch._grouped_mm(a, down_weight.transpose(1, 2), offs=ends)
+            _check(lib.pico_moe_combine_placed(_ptr(ys), _ptr(place), _ptr(out_w), T, top, D, _ptr(y), _ptr(base), code, st),
                    "moe_combine_placed")
             _count(3)
             return y
         except (RuntimeError, NotImplementedError):
             if torch.cuda.is_current_stream_capturing():
                 raise
-    act = torch.empty((n, ff), dtype=h.dtype, device=h.device)
+    a = torch.empty((n, ff), dtype=h.dtype, device=h.device)
     _check(lib.pico_moe_gemm(_ptr(h), _ptr(gate_up_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, ff, D,
-                             0, bm, _ptr(act), None, code, st), "moe_gemm (gate_up)")
+                             0 if gated else 2, bm, _ptr(a), None, _ptr(in_w), int(act), code, st), "moe_gemm (up)")
     out2 = torch.empty((n, D), dtype=torch.float32, device=h.device)
-    _check(lib.pico_moe_gemm(_ptr(act), _ptr(down_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, D, ff,
-                             1, bm, None, _ptr(out2), code, st), "moe_gemm (down)")
-    _check(lib.pico_moe_combine(_ptr(out2), _ptr(wgt), T, top, D, _ptr(y), code, st), "moe_combine")
+    _check(lib.pico_moe_gemm(_ptr(a), _ptr(down_weight), _ptr(offsets), _ptr(tile_start), _ptr(perm), n, E, top, D, ff,
+                             1, bm, None, _ptr(out2), None, 0, code, st), "moe_gemm (down)")
+    _check(lib.pico_moe_combine(_ptr(out2), _ptr(out_w), T, top, D, _ptr(y), _ptr(base), code, st), "moe_combine")
     _count(4)
+    return y
+
+
+def activation(u: torch.Tensor, act: int) -> torch.Tensor:
+    """In place on [n, ff]: silu (MOE_ACT_SILU) or relu squared (MOE_ACT_RELU2), float32 inside."""
+    _cuda(u)
+    if u.dim() != 2 or not u.is_contiguous():
+        raise KernelError("activation: u must be contiguous [n, ff]")
+    _check(library().pico_moe_scaled_act(_ptr(u), None, None, u.shape[0], u.shape[1], int(act), _ptr(u), _dtype_code(u),
+                                         _stream()), "activation")
+    _count()
+    return u
+
+
+# ------------------------------------------------------------------------------------------
+# Attention with normed queries and keys; linear attention with a state.
+def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor, inv_freq: torch.Tensor,
+                       mult: float, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                       slots: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                       n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, values_from_keys: bool) -> None:
+    """Per token row [q heads | k heads | v heads (absent with ``values_from_keys``) | anything]: adds the bias, stores the
+    values (with ``values_from_keys``: the biased keys before norm and rotation), RMS-norms every q and k head over
+    head_dim with the weights q_norm / k_norm (float32 [head_dim], shared by the heads; None: no norm), rotates the first
+    2 * len(inv_freq) dims of each head (dim i with i + len(inv_freq)) by position * inv_freq with cos and sin times
+    ``mult``, writes q back in place and k into its page.  float32 inside.  ``slots`` None: only q is treated."""
+    _cuda(qkv, bias, positions, inv_freq, q_norm, k_norm, slots, k_pages, v_pages)
+    T = qkv.shape[0]
+    cols = (n_heads + n_kv_heads * (1 if values_from_keys else 2)) * head_dim
+    if qkv.dim() != 2 or qkv.shape[1] < cols or qkv.stride(1) != 1:
+        raise KernelError(f"qk_norm_rope_store: rows must have at least {cols} contiguous columns")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] < cols or not bias.is_contiguous()):
+        raise KernelError("qk_norm_rope_store: bias must be float32 over the q, k (and v) columns")
+    for w in (q_norm, k_norm):
+        if w is not None and (w.dtype != torch.float32 or w.shape != (head_dim,)):
+            raise KernelError("qk_norm_rope_store: norm weights must be float32 [head_dim]")
+    if positions.dtype != torch.int32 or inv_freq.dtype != torch.float32 or 2 * inv_freq.shape[0] > head_dim:
+        raise KernelError("qk_norm_rope_store: positions int32, inv_freq float32 [<= head_dim / 2]")
+    if slots is not None:
+        if slots.dtype != torch.int32 or k_pages is None or v_pages is None:
+            raise KernelError("qk_norm_rope_store: slots must be int32 and come with pages")
+        for p in (k_pages, v_pages):
+            if p.dtype != qkv.dtype or not p.is_contiguous() or tuple(p.shape[1:]) != (n_kv_heads, page_size, head_dim):
+                raise KernelError("qk_norm_rope_store: pages must be contiguous [pages, kv_heads, page_size, head_dim] in qkv's dtype")
+    _check(library().pico_qk_norm_rope_store(_ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(positions), _ptr(inv_freq),
+                                             float(mult), _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(slots), _ptr(k_pages),
+                                             _ptr(v_pages), T, n_heads, n_kv_heads if slots is not None else 0, head_dim,
+                                             2 * inv_freq.shape[0], page_size, 1 if values_from_keys else 0,
+                                             _dtype_code(qkv), _stream()), f"qk_norm_rope_store (head_dim {head_dim})")
+    _count()
+
+
+def sigmoid_gate(o: torch.Tensor, gate_logits: torch.Tensor) -> torch.Tensor:
+    """In place: o[t, c] *= sigmoid(gate_logits[t, c]); gate_logits may be a column slice of a wider buffer."""
+    _cuda(o, gate_logits)
+    if o.dim() != 2 or not o.is_contiguous() or gate_logits.shape != o.shape or gate_logits.dtype != o.dtype \
+            or gate_logits.stride(1) != 1:
+        raise KernelError("sigmoid_gate: o contiguous [T, n], gate logits [T, n] of the same type with contiguous rows")
+    _check(library().pico_sigmoid_gate(_ptr(o), _ptr(gate_logits), gate_logits.stride(0), o.shape[0], o.shape[1],
+                                       _dtype_code(o), _stream()), "sigmoid_gate")
+    _count()
+    return o
+
+
+def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor,
+                           state: torch.Tensor, seg_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor,
+                           heads: int, dim: int, vdim: int, act: int = 1) -> torch.Tensor:
+    """Linear attention with a decay per head: per head S <- decay * S + k_t v_t^T, o_t = S^T q_t, token by token in
+    the order of each segment, from and into ``state`` float32 [slots, heads, vdim, dim] (row ``seg_slots[s]`` for
+    segment s; S stored transposed).  q, k, v of a token lie in its row of ``proj`` at q_off + h * dim, k_off + h * dim,
+    v_off + h * vdim and pass through silu (``act`` 1) or nothing (0) in float32.  A segment whose first position is
+    negative is padding.  Returns o float32 [T, heads * vdim]."""
+    _cuda(proj, decay, state, seg_slots, cu_q, positions)
+    T = proj.shape[0]
+    S = seg_slots.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1 or max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim) > proj.shape[1]:
+        raise KernelError("decay_linear_attention: the projection row is narrower than its parts")
+    if decay.dtype != torch.float32 or decay.shape != (heads,):
+        raise KernelError("decay_linear_attention: decay must be float32 [heads]")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, vdim, dim):
+        raise KernelError("decay_linear_attention: state must be contiguous float32 [slots, heads, vdim, dim]")
+    for t in (seg_slots, cu_q, positions):
+        if t.dtype != torch.int32:
+            raise KernelError("decay_linear_attention: index tensors must be int32")
+    if cu_q.shape[0] != S + 1 or positions.shape[0] != T:
+        raise KernelError("decay_linear_attention: cu_q must have one more entry than seg_slots, positions one per token")
+    out = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
+    _check(library().pico_decay_linear_attention(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(state),
+                                                 _ptr(seg_slots), _ptr(cu_q), _ptr(positions), _ptr(out), S, heads, dim,
+                                                 vdim, int(act), _dtype_code(proj), _stream()),
+           f"decay_linear_attention (dim {dim})")
+    _count()
+    return out
+
+
+def gated_rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], gate_logits: Optional[torch.Tensor], eps: float,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """y = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate_logits) over whole rows; x float32 [T, N]; weight float32
+    [N] or None; gate_logits [T, N] in ``out_dtype`` (may be a column slice) or None.  Returns [T, N] in ``out_dtype``."""
+    _cuda(x, weight, gate_logits)
+    T, N = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("gated_rms_norm: x must be contiguous float32 [T, N]")
+    if weight is not None and (weight.dtype != torch.float32 or weight.shape != (N,)):
+        raise KernelError("gated_rms_norm: weight must be float32 [N]")
+    if gate_logits is not None and (gate_logits.shape != (T, N) or gate_logits.dtype != out_dtype or gate_logits.stride(1) != 1):
+        raise KernelError("gated_rms_norm: gate logits must be [T, N] in the output type with contiguous rows")
+    y = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    _check(library().pico_gated_rms_norm(_ptr(x), _ptr(weight), _ptr(gate_logits),
+                                         gate_logits.stride(0) if gate_logits is not None else 0, float(eps), _ptr(y), T, N,
+                                         _dtype_code(y), _stream()), "gated_rms_norm")
+    _count()
     return y
 
 

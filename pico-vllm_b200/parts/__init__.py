@@ -1,8 +1,9 @@
 from .base import Param, Piece, Part, PagedKV, PagedTensors, PagedLatent, FixedState, CacheView, StepShape, MixerPlan
 from .registry import register, make, MIXERS, FEED_FORWARDS, NORMS, POSITIONS
-from .norm import RMSNorm, CentredNorm, NormedDelta
-from .rotary import Rotary, NoPosition
-from .attention import GQAAttention
+from .norm import RMSNorm, CentredNorm, NormedDelta, PassNorm
+from .rotary import Rotary, NoPosition, YarnRotary
+from .attention import GQAAttention, QKNormAttention
+from .linear_attention import DecayLinearAttention
 from .latent_attention import LatentAttention
 from .mlp import GatedMLP
 from .moe import RoutedExperts
@@ -12,4 +13,5 @@ from .block import PreNormBlock, SandwichBlock
 __all__ = ["Param", "Piece", "Part", "PagedKV", "PagedTensors", "FixedState", "CacheView", "StepShape", "MixerPlan", "register", "make", "MIXERS",
            "FEED_FORWARDS", "NORMS", "POSITIONS", "RMSNorm", "Rotary", "NoPosition", "GQAAttention",
            "GatedMLP", "TokenEmbedding", "OutputHead", "PreNormBlock", "PagedLatent", "CentredNorm", "NormedDelta",
-           "LatentAttention", "RoutedExperts", "SandwichBlock"]
+           "LatentAttention", "RoutedExperts", "SandwichBlock", "PassNorm", "YarnRotary", "QKNormAttention",
+           "DecayLinearAttention"]

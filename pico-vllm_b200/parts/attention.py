@@ -15,6 +15,7 @@ from typing import List, Optional
 import torch
 
 from .. import ops
+from ..errors import KernelError
 from .base import CacheView, MixerPlan, PagedKV, Param, Part, Piece, StepShape
 from .registry import register
 
@@ -142,3 +143,95 @@ class GQAAttention(Part):
             ops.skinny_linear_residual(out, self.o_weight, residual)
             return None
         return ops.linear(out, self.o_weight)
+
+
+def _linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """A handful of tokens: the weight-streaming kernel; more: the library product."""
+    if ops.skinny_takes(x, weight):
+        return ops.skinny_linear(x, weight)
+    return ops.linear(x, weight)
+
+
+@register("mixer", "qk_norm_attention")
+class QKNormAttention(Part):
+    """Grouped-query softmax attention with a per-head RMS norm on queries and keys before the rotation, an optional
+    soft cap on the scores, an optional sigmoid output gate, and - ``values_from_keys`` - no value projection: the
+    values are the keys as projected (bias added), before norm and rotation.
+
+        q = W_q h + b_q, k = W_k h + b_k            v = k  (or W_v h + b_v)
+        q' = rot(rms(q) * w_q), k' = rot(rms(k) * w_k)        (norm over head_dim, one weight shared by the heads)
+        s = scale * q' . k'(j);  s <- cap * tanh(s / cap);  p = softmax over j <= i (the last ``window`` keys, if any)
+        out = W_o ( concat_heads(sum_j p(j) v(j)) * sigmoid(W_g h) )
+
+    Launches: one product for q, k, (v) and the gate logits -> norm, rotation and cache store (one kernel) -> paged
+    attention -> gate -> output product.  Norms, angles, scores and the softmax are float32."""
+
+    def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position: Part, eps: float,
+                 scale: Optional[float] = None, softcap: Optional[float] = None, qk_norm: bool = True,
+                 qk_bias: bool = True, values_from_keys: bool = False, gate: bool = False, window: Optional[int] = None):
+        self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
+        self.position, self.eps, self.window = position, float(eps), window
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        self.softcap = float(softcap) if softcap else None
+        self.qk_norm, self.has_bias, self.values_from_keys, self.has_gate = qk_norm, qk_bias, values_from_keys, gate
+        self.proj_weight = self.proj_bias = self.q_norm = self.k_norm = self.o_weight = None
+
+    def params(self) -> List[Param]:
+        q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        proj = [Piece("q.weight", (q, self.width)), Piece("k.weight", (kv, self.width))]
+        bias = [Piece("q.bias", (q,)), Piece("k.bias", (kv,))]
+        if not self.values_from_keys:
+            proj.append(Piece("v.weight", (kv, self.width)))
+            bias.append(Piece("v.bias", (kv,)))
+        if self.has_gate:
+            proj.append(Piece("g.weight", (q, self.width)))
+        ps = [Param("proj_weight", tuple(proj)), Param("o_weight", (Piece("o.weight", (self.width, q)),))]
+        if self.has_bias:
+            ps.append(Param("proj_bias", tuple(bias), kind="vector"))
+        if self.qk_norm:
+            ps += [Param("q_norm", (Piece("q.norm", (self.head_dim,)),), kind="vector", init="one_plus_normal"),
+                   Param("k_norm", (Piece("k.norm", (self.head_dim,)),), kind="vector", init="one_plus_normal")]
+        return ps
+
+    def cache_spec(self):
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
+
+    def materialize(self, device, dtype):
+        self.position.materialize(device, dtype)
+
+    def plan_key(self):
+        return ("qk_norm_attention", self.n_heads, self.n_kv_heads, self.head_dim, self.window)
+
+    def plan(self, shape: StepShape) -> AttentionPlan:
+        splits = decode_splits(shape, self.n_kv_heads)
+        scratch = ops.attention_scratch_floats(shape.num_tokens, self.n_heads, self.head_dim, splits)
+        return AttentionPlan(key=(splits, 0), scratch_floats=scratch, splits=splits, pair_min_keys=0)
+
+    def forward(self, h: torch.Tensor, batch, cache: CacheView) -> torch.Tensor:
+        gb = batch.groups[cache.group]
+        slots = gb.slots if cache.store else None
+        H, G, d = self.n_heads, self.n_kv_heads, self.head_dim
+        pairing = getattr(self.position, "pairing", "rot_half")
+        rot = 2 * self.position.inv_freq.shape[0]
+        if pairing not in ("rot_half",) and not (pairing == "half" and rot in (0, d)):
+            raise KernelError(f"qk_norm_attention: rotary pairing {pairing!r} is not built")
+        proj = _linear(h, self.proj_weight)                      # [T, q | k | (v) | (gate logits)]
+        ops.qk_norm_rope_store(proj, self.proj_bias, batch.positions, self.position.inv_freq,
+                               getattr(self.position, "mult", 1.0), self.q_norm, self.k_norm, self.eps, slots, cache.k,
+                               cache.v, H, G, d, cache.page_size, self.values_from_keys)
+        out = torch.empty((h.shape[0], H * d), dtype=h.dtype, device=h.device)
+        plan = batch.plan(self)
+        splits = plan.splits if plan is not None else 1
+        if ops.mma_attention_takes(h.dtype, H, G, d):
+            ops.paged_attention_mma(proj, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
+                                    batch.cu_q, batch.prefill_segs, batch.num_prefill_segs, batch.max_prefill_q,
+                                    batch.decode_tokens, batch.num_decode_tokens, H, G, d, cache.page_size, self.window,
+                                    self.scale, splits, batch.scratch, cache.k_map, cache.v_map, cache.k_map2d,
+                                    cache.v_map2d, 0, softcap=self.softcap)
+        else:       # float32, or sizes the tensor-core kernels do not take
+            ops.paged_attention(proj, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table, H, G, d,
+                                cache.page_size, self.window, self.scale, splits, batch.scratch, softcap=self.softcap)
+        if self.has_gate:
+            g0 = (H + G * (1 if self.values_from_keys else 2)) * d
+            ops.sigmoid_gate(out, proj[:, g0:g0 + H * d])
+        return _linear(out, self.o_weight)

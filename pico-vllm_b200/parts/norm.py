@@ -44,13 +44,21 @@ class RMSNorm(Part):
     plain_rms = True
     norm_kind = ops.NORM_RMS
 
-    def __init__(self, width: int, eps: float):
-        self.width, self.eps = width, eps
+    def __init__(self, width: int, eps: float, one_plus: bool = False):
+        """``one_plus``: the stored tensor lies around zero and the norm multiplies by 1 + it (added once, in float32,
+        when the tensor is loaded; the kernels see an ordinary weight)."""
+        self.width, self.eps, self.one_plus = width, eps, one_plus
         self.weight: Optional[torch.Tensor] = None
         self.act_dtype = torch.bfloat16
 
     def params(self) -> List[Param]:
-        return [Param("weight", (Piece("weight", (self.width,)),), kind="vector", init="one_plus_normal")]
+        return [Param("weight", (Piece("weight", (self.width,)),), kind="vector",
+                      init="normal" if self.one_plus else "one_plus_normal")]
+
+    def assign(self, attr: str, tensor: torch.Tensor) -> None:
+        if attr == "weight" and self.one_plus:
+            tensor = tensor.to(torch.float32) + 1.0
+        setattr(self, attr, tensor)
 
     def materialize(self, device, dtype):
         self.act_dtype = dtype
@@ -87,3 +95,32 @@ class CentredNorm(Part):
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """As :meth:`RMSNorm.add_norm`; ``delta`` may be a :class:`NormedDelta`."""
         return _post_add_norm(self, ops.NORM_CENTRED, x, delta, rows)
+
+
+@register("norm", "none")
+class PassNorm(Part):
+    """No norm at all: ``add_norm`` adds what is pending to the residual stream and hands the stream on in the
+    activation type - the input norm of a layer whose sublayers read the stream itself.  In float32 the stream is
+    handed on as it is (readers must not write to it)."""
+    norm_kind = ops.NORM_COPY
+    weight = None
+    eps = 0.0
+
+    def __init__(self, width: int):
+        self.width = width
+        self.act_dtype = torch.bfloat16
+
+    def materialize(self, device, dtype):
+        self.act_dtype = dtype
+
+    def add_norm(self, x: torch.Tensor, delta: Union[None, torch.Tensor, NormedDelta],
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is None and self.act_dtype == torch.float32:
+            post = None
+            if isinstance(delta, NormedDelta):
+                post, delta = delta.norm, delta.delta
+            if delta is not None:
+                ops.post_add_norm(x, delta, None if post is None else post.weight, 0 if post is None else post.norm_kind,
+                                  0.0 if post is None else post.eps, None, ops.NORM_NONE, 0.0, None, None)
+            return x
+        return _post_add_norm(self, ops.NORM_COPY, x, delta, rows)

@@ -45,6 +45,9 @@ def _register_builtin() -> None:
     from .config.zapipel import ZapipelConfig
     from .models.zapipel import build_zapipel
     register_architecture("Zapipel", ZapipelConfig, build_zapipel)
+    from .config.zikupel import ZikupelConfig
+    from .models.zikupel import build_zikupel
+    register_architecture("Zikupel", ZikupelConfig, build_zikupel)
 
 
 _register_builtin()

@@ -76,7 +76,7 @@ def attention_scratch_floats(T, n_heads, head_dim, n_splits):
 
 
 def paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads,
-                    head_dim, page_size, window, scale, n_splits=1, scratch=None):
+                    head_dim, page_size, window, scale, n_splits=1, scratch=None, softcap=None):
     T = q.shape[0]
     g = n_heads // n_kv_heads
     for t in range(T):
@@ -92,6 +92,8 @@ def paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n
         qt = q[t, :n_heads * head_dim].float().view(n_heads, head_dim)
         for h in range(n_heads):
             s = (k[:, h // g, :] @ qt[h]) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
             pr = torch.softmax(s, dim=0)
             out[t, h * head_dim:(h + 1) * head_dim] = (pr @ v[:, h // g, :]).to(out.dtype)
     return out
@@ -105,9 +107,9 @@ def mma_attention_takes(dtype, n_heads, n_kv_heads, head_dim):
 def paged_attention_mma(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs,
                         n_prefill_segs, max_prefill_q, decode_tokens, n_decode_tokens, n_heads, n_kv_heads, head_dim,
                         page_size, window, scale, n_splits=1, scratch=None, k_map=None, v_map=None, k_map2d=None,
-                        v_map2d=None, pair_min_keys=0):
+                        v_map2d=None, pair_min_keys=0, softcap=None):
     return paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads, head_dim,
-                           page_size, window, scale)
+                           page_size, window, scale, softcap=softcap)
 
 
 SKINNY_MAX_TOKENS = 16
@@ -210,7 +212,7 @@ def sample(logits, temperature, top_p, uniform, out):
 
 # ------------------------------------------------------------------ norm -> add -> norm, latent attention, routed experts
 def _norm(u, kind, w, eps):
-    if kind == 0:
+    if kind in (0, 3):          # none; 3: no norm on the way out, the row is only written in the activation type
         return u
     if kind == 2:
         u = u - u.mean(-1, keepdim=True)
@@ -269,27 +271,106 @@ def head_scale(o, gate, heads):
     return o
 
 
-def moe_route(h, router_weight, router_bias, top):
+def moe_route(h, router_weight, router_bias, top, scoring=0):
     z = h.float() @ router_weight.t()
     if router_bias is not None:
         z = z + router_bias
     val, idx = torch.topk(z, top, dim=-1)
-    return idx.to(torch.int32), torch.softmax(val, dim=-1)
+    return idx.to(torch.int32), (torch.sigmoid(val) if scoring == 1 else torch.softmax(val, dim=-1))
 
 
-def moe_experts(h, idx, wgt, gate_up_weight, down_weight):
-    ff = gate_up_weight.shape[1] // 2
-    y = torch.zeros(h.shape, dtype=torch.float32)
+def _act(u, act):
+    return torch.relu(u) ** 2 if act == 1 else u * torch.sigmoid(u)
+
+
+def moe_experts(h, idx, wgt, gate_up_weight, down_weight, gated=True, act=0, weight_on_input=False, base=None):
+    ff = gate_up_weight.shape[1] // 2 if gated else gate_up_weight.shape[1]
+    y = torch.zeros(h.shape, dtype=torch.float32) if base is None else base.float().clone()
     for t in range(h.shape[0]):
         for j in range(idx.shape[1]):
             e = int(idx[t, j])
-            gu = gate_up_weight[e].float() @ h[t].float()
-            g, u = gu[:ff], gu[ff:]
-            y[t] += wgt[t, j] * (down_weight[e].float() @ (g * torch.sigmoid(g) * u))
+            if gated:
+                gu = gate_up_weight[e].float() @ h[t].float()
+                g, u = gu[:ff], gu[ff:]
+                y[t] += wgt[t, j] * (down_weight[e].float() @ (g * torch.sigmoid(g) * u))
+            elif weight_on_input:
+                y[t] += down_weight[e].float() @ _act(gate_up_weight[e].float() @ (wgt[t, j] * h[t].float()), act)
+            else:
+                y[t] += wgt[t, j] * (down_weight[e].float() @ _act(gate_up_weight[e].float() @ h[t].float(), act))
     return y.to(h.dtype)
 
 
-NAMES = ["post_add_norm", "scale_softcap", "latent_norm_store", "head_linear", "head_scale", "moe_route", "moe_experts",
+def activation(u, act):
+    u.copy_(_act(u.float(), act).to(u.dtype))
+    return u
+
+
+def qk_norm_rope_store(qkv, bias, positions, inv_freq, mult, q_norm, k_norm, eps, slots, k_pages, v_pages, n_heads,
+                       n_kv_heads, head_dim, page_size, values_from_keys):
+    T = qkv.shape[0]
+    nq, nk = n_heads * head_dim, n_kv_heads * head_dim
+    cols = nq + nk * (1 if values_from_keys else 2)
+    x = qkv[:, :cols].float()
+    if bias is not None:
+        x = x + bias[:cols]
+    q = x[:, :nq].view(T, n_heads, head_dim)
+    k = x[:, nq:nq + nk].view(T, n_kv_heads, head_dim)
+    v = k if values_from_keys else x[:, nq + nk:].view(T, n_kv_heads, head_dim)
+    r = inv_freq.shape[0]
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    cos, sin = (ang.cos() * mult)[:, None, :], (ang.sin() * mult)[:, None, :]
+
+    def treat(u, w):
+        if w is not None:
+            u = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * w
+        a, b = u[..., :r], u[..., r:2 * r]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin, u[..., 2 * r:]], dim=-1)
+    live = positions >= 0
+    qn = torch.where(live[:, None, None], treat(q, q_norm), q)
+    qkv[:, :nq] = qn.reshape(T, nq).to(qkv.dtype)
+    if slots is None:
+        return
+    kn = treat(k, k_norm)
+    for t, s in enumerate(slots.tolist()):
+        if s >= 0 and bool(live[t]):
+            k_pages[s // page_size, :, s % page_size, :] = kn[t].to(k_pages.dtype)
+            v_pages[s // page_size, :, s % page_size, :] = v[t].to(v_pages.dtype)
+
+
+def sigmoid_gate(o, gate_logits):
+    o.copy_((o.float() * torch.sigmoid(gate_logits.float())).to(o.dtype))
+    return o
+
+
+def decay_linear_attention(proj, q_off, k_off, v_off, decay, state, seg_slots, cu_q, positions, heads, dim, vdim, act=1):
+    T = proj.shape[0]
+    p = proj.float()
+    f = (lambda u: u * torch.sigmoid(u)) if act == 1 else (lambda u: u)
+    q = f(p[:, q_off:q_off + heads * dim]).view(T, heads, dim)
+    k = f(p[:, k_off:k_off + heads * dim]).view(T, heads, dim)
+    v = f(p[:, v_off:v_off + heads * vdim]).view(T, heads, vdim)
+    out = torch.zeros((T, heads * vdim), dtype=torch.float32)
+    for s in range(seg_slots.shape[0]):
+        b, e = int(cu_q[s]), int(cu_q[s + 1])
+        if e <= b or int(positions[b]) < 0:
+            continue
+        S = state[int(seg_slots[s])]                            # [heads, vdim, dim]: transposed
+        for t in range(b, e):
+            S.mul_(decay[:, None, None]).add_(v[t][:, :, None] * k[t][:, None, :])
+            out[t] = torch.einsum("hvd,hd->hv", S, q[t]).reshape(-1)
+    return out
+
+
+def gated_rms_norm(x, weight, gate_logits, eps, out_dtype):
+    y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight
+    if gate_logits is not None:
+        y = y * torch.sigmoid(gate_logits.float())
+    return y.to(out_dtype)
+
+
+NAMES = ["activation", "qk_norm_rope_store", "sigmoid_gate", "decay_linear_attention", "gated_rms_norm", "post_add_norm", "scale_softcap", "latent_norm_store", "head_linear", "head_scale", "moe_route", "moe_experts",
          "embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
          "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "make_kv_tensor_map_2d", "tc_takes", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
