@@ -173,13 +173,14 @@ __device__ __forceinline__ void tca_softmax_sync() { asm volatile("bar.sync 2, 2
 #define TCA_COL_O 192
 #define TCA_COL_Q 448          // the queries as a tensor-memory operand: 64 columns of bfloat16 pairs at head size 128
 
-template <int HD>      // head size, a multiple of 64 up to 128
+// CAP: the scaled scores pass through a soft cap c * tanh(s / c) before the softmax (cap_log2 = c log2 e, cap_2x = 2 scale / c)
+template <int HD, bool CAP>      // head size, a multiple of 64 up to 128
 __global__ void __launch_bounds__(TCA_THREADS)
 paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
                              const int* __restrict__ seg_list, const int* __restrict__ cu_q,
                              const int* __restrict__ positions, const int* __restrict__ block_table, int table_stride,
-                             int nh, int nkv, int page_size, int window, float scale_log2,
+                             int nh, int nkv, int page_size, int window, float scale_log2, float cap_log2, float cap_2x,
                              float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                              size_t n_rows, int n_parts, int split_min) {
     pdl_launch_dependents();
@@ -434,7 +435,10 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                 for (int i = 0; i < 4; ++i)
                     mx4[i] = tca_max3(mx4[i], __uint_as_float(sv[c + 2 * i]), __uint_as_float(sv[c + 2 * i + 1]));
             }
-            const float mx = fmaxf(tca_max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * scale_log2;
+            const float mx_raw = fmaxf(tca_max3(mx4[0], mx4[1], mx4[2]), mx4[3]);
+            // the cap is monotonic, so the capped maximum is the cap of the maximum; a row with no visible key stays at -inf
+            const float mx = CAP ? (mx_raw == -INFINITY ? -INFINITY : pico_score_log2(mx_raw, scale_log2, cap_log2, cap_2x))
+                                 : mx_raw * scale_log2;
             // the maximum in use moves only when the true one has grown by more than 2^8: the same
             // value is used for the probabilities and for the sum, so the result is exact
             const bool grow = mx > m_use + TCA_RESCALE_AT;
@@ -449,7 +453,12 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
                 float x0, x1;
-                tca_unpack(tca_fma2(tca_pack(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+                if (CAP) {
+                    const float r0 = __uint_as_float(sv[c]), r1 = __uint_as_float(sv[c + 1]);
+                    x0 = r0 == -INFINITY ? -INFINITY : pico_score_log2(r0, scale_log2, cap_log2, cap_2x) + neg_m;
+                    x1 = r1 == -INFINITY ? -INFINITY : pico_score_log2(r1, scale_log2, cap_log2, cap_2x) + neg_m;
+                } else
+                    tca_unpack(tca_fma2(tca_pack(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
                 const float p0 = tca_exp2(x0), p1 = tca_exp2(x1);
                 sum2[(c >> 1) & 1] = tca_add2(sum2[(c >> 1) & 1], tca_pack(p0, p1));
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
@@ -686,7 +695,7 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
                                         const int* seg_list, int n_segs, const int* cu_q, int max_q_len,
                                         const int* positions, const int* block_table, int table_stride, int nh, int nkv,
                                         int hd, int page_size, int window, float scale, int pair_min_keys, float* scratch,
-                                        int n_tokens, int* counters, int n_counters, cudaStream_t stream) {
+                                        int n_tokens, int* counters, int n_counters, float softcap, cudaStream_t stream) {
     if (n_segs <= 0 || max_q_len <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
@@ -702,19 +711,20 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
     float* part_ml = scratch ? scratch + 2 * n_rows * hd : nullptr;
     const dim3 grid(n_qt * n_parts, nkv, n_segs);
     const float scale_log2 = scale * 1.4426950408889634f;
+    const float cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, cap_2x = softcap > 0.f ? 2.0f * scale / softcap : 0.f;
     const size_t smem = (size_t)TCA_STAGES * 2 * TCA_BN * hd * 2 + (4 * TCA_STAGES + 9) * 8 + 16 + 2 * TCA_BM * 8 + TCA_TABLE_CACHE * 4 + 1024;
     CUtensorMap km, vm;
     memcpy(&km, k_map, sizeof(CUtensorMap));
     memcpy(&vm, v_map, sizeof(CUtensorMap));
-#define LAUNCH_TCA(HD)                                                                                                   \
+#define LAUNCH_TCA(HD, CAP)                                                                                              \
     do {                                                                                                                 \
-        cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-        pico_launch((paged_prefill_tcgen05_kernel<HD>), grid, dim3(TCA_THREADS), smem, stream, km, vm, (const bf16*)q,   \
+        cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<HD, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        pico_launch((paged_prefill_tcgen05_kernel<HD, CAP>), grid, dim3(TCA_THREADS), smem, stream, km, vm, (const bf16*)q, \
                     q_row_stride, (bf16*)out, seg_list, cu_q, positions, block_table, table_stride, nh, nkv, page_size,  \
-                    window, scale_log2, part_o, part_ml, counters, n_rows, n_parts, split_min);                          \
+                    window, scale_log2, cap_log2, cap_2x, part_o, part_ml, counters, n_rows, n_parts, split_min);        \
     } while (0)
-    if (hd == 64) LAUNCH_TCA(64);
-    else LAUNCH_TCA(128);
+    if (hd == 64) { if (cap_log2 > 0.f) LAUNCH_TCA(64, true); else LAUNCH_TCA(64, false); }
+    else { if (cap_log2 > 0.f) LAUNCH_TCA(128, true); else LAUNCH_TCA(128, false); }
 #undef LAUNCH_TCA
     return pico_launch_status();
 }

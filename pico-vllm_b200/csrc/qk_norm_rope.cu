@@ -4,7 +4,8 @@
 //   row of a token: [ q heads (nh x hd) | k heads (nkv x hd) | v heads (nkv x hd, absent when the values are the keys) ]
 //   u  = row + bias                                                     (float32 from here on)
 //   v  = the v head of the row, or - values_from_keys - the k head u itself, before norm and rotation
-//   u' = u / sqrt(mean(u^2) + eps) * w_q (or w_k), one weight of hd elements shared by the heads  (skipped without weights)
+//   u' = u / sqrt(mean(u^2) + eps) * w_q (or w_k), one weight of hd elements shared by the heads  (skipped without weights);
+//        the mean is over norm_dim <= hd elements: a head padded with zeros to the next size the attention kernels take
 //   dims i and i + rot_dim/2 (i < rot_dim/2) turn by the angle position * inv_freq[i]; cos and sin are multiplied
 //   by `mult` (a position scaling's attention factor; 1 without); dims from rot_dim on pass unchanged
 //   q' is written back in place; k' and v go to their pages and are not written back.
@@ -21,7 +22,7 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, int row_stride, const float* __r
                           const int* __restrict__ positions, const float* __restrict__ inv_freq, float mult,
                           const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                           const int* __restrict__ slots, TA* __restrict__ k_pages, TA* __restrict__ v_pages, int nh,
-                          int nkv, int hd, int rot_half, int page_size, int values_from_keys) {
+                          int nkv, int hd, int norm_dim, int rot_half, int page_size, int values_from_keys) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float qsm[];          // cos[rot_half], sin[rot_half], then hd floats per warp
@@ -69,7 +70,7 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, int row_stride, const float* __r
         }
         const float* w = is_q ? q_w : k_w;
         if (w) {
-            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
+            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)norm_dim + eps);
 #pragma unroll
             for (int j = 0; j < QKN_MAX_DPL; ++j) {
                 const int d = lane + 32 * j;
@@ -110,9 +111,10 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, int row_stride, const float* __r
 PICO_API int pico_qk_norm_rope_store(void* qkv, int row_stride, const float* bias, const int* positions,
                                      const float* inv_freq, float mult, const float* q_w, const float* k_w, float eps,
                                      const int* slots, void* k_pages, void* v_pages, int T, int nh, int nkv, int hd,
-                                     int rot_dim, int page_size, int values_from_keys, int dtype, cudaStream_t stream) {
+                                     int norm_dim, int rot_dim, int page_size, int values_from_keys, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (hd < 1 || hd > 32 * QKN_MAX_DPL || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || nh < 1 || nkv < 0)
+    if (hd < 1 || hd > 32 * QKN_MAX_DPL || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || nh < 1 || nkv < 0 || norm_dim < 1 ||
+        norm_dim > hd)
         return PICO_ERR_SIZE;
     const int heads = nh + nkv;
     const int warps = heads < 8 ? heads : 8;
@@ -120,11 +122,11 @@ PICO_API int pico_qk_norm_rope_store(void* qkv, int row_stride, const float* bia
     if (dtype == PICO_F32)
         pico_launch((qk_norm_rope_store_kernel<float>), dim3(T), dim3(warps * 32), smem, stream, (float*)qkv, row_stride,
                     bias, positions, inv_freq, mult, q_w, k_w, eps, slots, (float*)k_pages, (float*)v_pages, nh, nkv, hd,
-                    rot_dim / 2, page_size, values_from_keys);
+                    norm_dim, rot_dim / 2, page_size, values_from_keys);
     else if (dtype == PICO_BF16)
         pico_launch((qk_norm_rope_store_kernel<bf16>), dim3(T), dim3(warps * 32), smem, stream, (bf16*)qkv, row_stride,
                     bias, positions, inv_freq, mult, q_w, k_w, eps, slots, (bf16*)k_pages, (bf16*)v_pages, nh, nkv, hd,
-                    rot_dim / 2, page_size, values_from_keys);
+                    norm_dim, rot_dim / 2, page_size, values_from_keys);
     else
         return PICO_ERR_DTYPE;
     return pico_launch_status();

@@ -70,7 +70,7 @@ def library():
         "pico_tma_status": [vp],
         "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32, i32],
         "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32,
-                                       vp, i32, vp, i32, vp],
+                                       vp, i32, vp, i32, f32, vp],
         "pico_tca_status": [vp],
         "pico_gemm_tcgen05_pair": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
         "pico_tp_status": [vp],
@@ -88,7 +88,7 @@ def library():
         "pico_moe_combine": [vp, vp, i32, i32, i32, vp, vp, i32, vp],
         "pico_moe_scaled_act": [vp, vp, vp, i32, i32, i32, vp, i32, vp],
         "pico_qk_norm_rope_store": [vp, i32, vp, vp, vp, f32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
-                                    i32, vp],
+                                    i32, i32, vp],
         "pico_sigmoid_gate": [vp, vp, i32, i32, i32, i32, vp],
         "pico_decay_linear_attention": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
         "pico_gated_rms_norm": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
@@ -399,8 +399,6 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     lib = library()
     win = int(window) if window else 0
     cap = float(softcap) if softcap else 0.0
-    if cap > 0.0:
-        k_map2d = v_map2d = None        # the tcgen05 prompt kernel has no soft cap: portions take the mma.sync kernel
     if n_prefill_segs > 0 and k_map2d is not None and v_map2d is not None:
         # pair_min_keys > 0 (and scratch for two partial results per (token, head)): every query tile gets two
         # blocks, which share it when it sees at least that many keys; the pairs' counters are zero between launches
@@ -414,7 +412,7 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                                               n_kv_heads, head_dim, page_size, win, float(scale),
                                               int(pair_min_keys) if split else 0, _ptr(scratch) if split else None, T,
                                               _ptr(counters) if split else None, counters.numel() if split else 0,
-                                              _stream()),
+                                              cap, _stream()),
                f"paged_prefill_tcgen05 (head_dim {head_dim})")
         _count()
     elif n_prefill_segs > 0:
@@ -958,12 +956,14 @@ def activation(u: torch.Tensor, act: int) -> torch.Tensor:
 def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor, inv_freq: torch.Tensor,
                        mult: float, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
                        slots: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-                       n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, values_from_keys: bool) -> None:
+                       n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, values_from_keys: bool,
+                       norm_dim: Optional[int] = None) -> None:
     """Per token row [q heads | k heads | v heads (absent with ``values_from_keys``) | anything]: adds the bias, stores the
     values (with ``values_from_keys``: the biased keys before norm and rotation), RMS-norms every q and k head over
     head_dim with the weights q_norm / k_norm (float32 [head_dim], shared by the heads; None: no norm), rotates the first
     2 * len(inv_freq) dims of each head (dim i with i + len(inv_freq)) by position * inv_freq with cos and sin times
-    ``mult``, writes q back in place and k into its page.  float32 inside.  ``slots`` None: only q is treated."""
+    ``mult``, writes q back in place and k into its page.  float32 inside.  ``slots`` None: only q is treated.
+    ``norm_dim``: the number of elements the norm's mean is taken over (heads padded with zeros up to head_dim)."""
     _cuda(qkv, bias, positions, inv_freq, q_norm, k_norm, slots, k_pages, v_pages)
     T = qkv.shape[0]
     cols = (n_heads + n_kv_heads * (1 if values_from_keys else 2)) * head_dim
@@ -985,7 +985,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], position
     _check(library().pico_qk_norm_rope_store(_ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(positions), _ptr(inv_freq),
                                              float(mult), _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(slots), _ptr(k_pages),
                                              _ptr(v_pages), T, n_heads, n_kv_heads if slots is not None else 0, head_dim,
-                                             2 * inv_freq.shape[0], page_size, 1 if values_from_keys else 0,
+                                             int(norm_dim or head_dim), 2 * inv_freq.shape[0], page_size, 1 if values_from_keys else 0,
                                              _dtype_code(qkv), _stream()), f"qk_norm_rope_store (head_dim {head_dim})")
     _count()
 

@@ -171,6 +171,7 @@ class QKNormAttention(Part):
                  qk_bias: bool = True, values_from_keys: bool = False, gate: bool = False, window: Optional[int] = None):
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
         self.position, self.eps, self.window = position, float(eps), window
+        self.row = -(-head_dim // 16) * 16           # a head in the kernels: padded with zeros to a multiple of 16
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
         self.softcap = float(softcap) if softcap else None
         self.qk_norm, self.has_bias, self.values_from_keys, self.has_gate = qk_norm, qk_bias, values_from_keys, gate
@@ -193,32 +194,48 @@ class QKNormAttention(Part):
                    Param("k_norm", (Piece("k.norm", (self.head_dim,)),), kind="vector", init="one_plus_normal")]
         return ps
 
+    def assign(self, attr: str, tensor: torch.Tensor) -> None:
+        """A head size that is no multiple of 16 is padded with zeros, head by head: rows of the projections, the biases
+        and the norm weights, columns of the output matrix.  Padded dimensions are zero in q, k and v and change nothing."""
+        d, r = self.head_dim, self.row
+        if r != d:
+            if attr in ("proj_weight", "proj_bias"):
+                tail = tensor.shape[1:]
+                t = tensor.view(-1, d, *tail)
+                tensor = torch.cat([t, t.new_zeros((t.shape[0], r - d) + tuple(tail))], 1).reshape(-1, *tail)
+            elif attr in ("q_norm", "k_norm"):
+                tensor = torch.cat([tensor, tensor.new_zeros(r - d)])
+            elif attr == "o_weight":
+                t = tensor.view(self.width, self.n_heads, d)
+                tensor = torch.cat([t, t.new_zeros(self.width, self.n_heads, r - d)], 2).reshape(self.width, -1)
+        setattr(self, attr, tensor.contiguous())
+
     def cache_spec(self):
-        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
+        return PagedKV(self.n_kv_heads, self.row, self.window)
 
     def materialize(self, device, dtype):
         self.position.materialize(device, dtype)
 
     def plan_key(self):
-        return ("qk_norm_attention", self.n_heads, self.n_kv_heads, self.head_dim, self.window)
+        return ("qk_norm_attention", self.n_heads, self.n_kv_heads, self.row, self.window)
 
     def plan(self, shape: StepShape) -> AttentionPlan:
         splits = decode_splits(shape, self.n_kv_heads)
-        scratch = ops.attention_scratch_floats(shape.num_tokens, self.n_heads, self.head_dim, splits)
+        scratch = ops.attention_scratch_floats(shape.num_tokens, self.n_heads, self.row, splits)
         return AttentionPlan(key=(splits, 0), scratch_floats=scratch, splits=splits, pair_min_keys=0)
 
     def forward(self, h: torch.Tensor, batch, cache: CacheView) -> torch.Tensor:
         gb = batch.groups[cache.group]
         slots = gb.slots if cache.store else None
-        H, G, d = self.n_heads, self.n_kv_heads, self.head_dim
+        H, G, d = self.n_heads, self.n_kv_heads, self.row
         pairing = getattr(self.position, "pairing", "rot_half")
         rot = 2 * self.position.inv_freq.shape[0]
-        if pairing not in ("rot_half",) and not (pairing == "half" and rot in (0, d)):
+        if pairing not in ("rot_half",) and not (pairing == "half" and rot in (0, self.head_dim)):
             raise KernelError(f"qk_norm_attention: rotary pairing {pairing!r} is not built")
         proj = _linear(h, self.proj_weight)                      # [T, q | k | (v) | (gate logits)]
         ops.qk_norm_rope_store(proj, self.proj_bias, batch.positions, self.position.inv_freq,
                                getattr(self.position, "mult", 1.0), self.q_norm, self.k_norm, self.eps, slots, cache.k,
-                               cache.v, H, G, d, cache.page_size, self.values_from_keys)
+                               cache.v, H, G, d, cache.page_size, self.values_from_keys, norm_dim=self.head_dim)
         out = torch.empty((h.shape[0], H * d), dtype=h.dtype, device=h.device)
         plan = batch.plan(self)
         splits = plan.splits if plan is not None else 1

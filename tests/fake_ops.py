@@ -306,7 +306,7 @@ def activation(u, act):
 
 
 def qk_norm_rope_store(qkv, bias, positions, inv_freq, mult, q_norm, k_norm, eps, slots, k_pages, v_pages, n_heads,
-                       n_kv_heads, head_dim, page_size, values_from_keys):
+                       n_kv_heads, head_dim, page_size, values_from_keys, norm_dim=None):
     T = qkv.shape[0]
     nq, nk = n_heads * head_dim, n_kv_heads * head_dim
     cols = nq + nk * (1 if values_from_keys else 2)
@@ -322,7 +322,7 @@ def qk_norm_rope_store(qkv, bias, positions, inv_freq, mult, q_norm, k_norm, eps
 
     def treat(u, w):
         if w is not None:
-            u = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * w
+            u = u / torch.sqrt((u * u).sum(-1, keepdim=True) / (norm_dim or head_dim) + eps) * w
         a, b = u[..., :r], u[..., r:2 * r]
         return torch.cat([a * cos - b * sin, b * cos + a * sin, u[..., 2 * r:]], dim=-1)
     live = positions >= 0

@@ -181,3 +181,50 @@ def forward(raw, tensors, ids, mem, start, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return norm_one_plus(x, tensors["final.norm"], eps) @ tensors["head"].T
+
+
+class PlainZikupel:
+    """The whole model over explicit per-sequence memory; ``forward`` may be called again with further tokens."""
+
+    def __init__(self, raw, tensors, dtype=torch.float64):
+        self.raw = raw
+        self.t = {k: v.to(dtype) for k, v in tensors.items()}
+        self.dtype = dtype
+
+    def new_state(self):
+        return {"mem": new_memory(self.raw, self.dtype), "n": 0, "margin": [], "top": []}
+
+    def forward(self, state, ids):
+        """Logits [len(ids), vocab]; the smallest router margin of every token is appended to state["margin"]."""
+        raw, eps = self.raw, self.raw["norm"]["eps"]
+        x = self.t["embed"][torch.as_tensor(ids, dtype=torch.long)]
+        margin = torch.full((len(ids),), float("inf"), dtype=self.dtype)
+        for i, layer in enumerate(raw["layers"]):
+            p = sub(self.t, f"l{i}.mix.")
+            if layer["type"] == "attention":
+                y = softmax_attention(x, state["mem"][i], state["n"], p, layer["mixer"], eps)
+            else:
+                y = linear_attention(x, state["mem"][i], p, layer["mixer"], eps)
+            x = x + norm_one_plus(y, self.t[f"l{i}.norm1"], eps)
+            f = layer.get("mlp")
+            if f is not None:
+                pf = sub(self.t, f"l{i}.mlp.")
+                if f["kind"] == "dense":
+                    y = dense_ff(x, pf)
+                else:
+                    margin = torch.minimum(margin, route_margin(x, pf["router"], f["router"]["top"]))
+                    y = moe_ff(x, pf, f)
+                x = x + norm_one_plus(y, self.t[f"l{i}.norm2"], eps)
+        state["n"] += len(ids)
+        state["margin"] += margin.tolist()
+        return norm_one_plus(x, self.t["final.norm"], eps) @ self.t["head"].T
+
+    def greedy(self, prompt, n):
+        st = self.new_state()
+        logits = self.forward(st, prompt)
+        out = []
+        for _ in range(n):
+            tok = int(logits[-1].argmax())
+            out.append(tok)
+            logits = self.forward(st, [tok])
+        return out
