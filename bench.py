@@ -547,6 +547,24 @@ DESIGN_SHAPES = {
 DESIGN_VOCAB = 32000
 
 
+def zikupel_config(shape, layers):
+    """The Zikupel design at the sizes of ``shape``: three layers of linear attention (as many heads, keys and values of
+    the head size, decays from fast to almost none) to one of softmax attention (half of every head turned, stretched
+    frequencies, capped scores); even layers have the dense feed-forward, odd layers route ``top`` of ``experts`` experts
+    (together as wide as the dense one) beside a shared expert of one expert's size."""
+    import math
+    s = DESIGN_SHAPES[shape]
+    H, d = s["heads"], s["head"]
+    att = dict(heads=H, kv_heads=s["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, softcap=30.0,
+               rot=dict(base=10000.0, dims=d // 2, scaling=dict(factor=4.0, original=1024, fast=32.0, slow=1.0)))
+    lin = dict(heads=H, dim=d, vdim=d, decay=[math.exp(-2.0 ** (-1 - 8.0 * h / H)) for h in range(H)])
+    moe = dict(kind="moe", expert=dict(ff=s["ff"] // s["top"]), router=dict(experts=s["experts"], top=s["top"]),
+               shared=dict(ff=s["ff"] // s["top"]))
+    zl = [dict(type="attention" if i % 4 == 3 else "lightning", mixer=dict(att if i % 4 == 3 else lin),
+               mlp=dict(kind="dense", ff=s["ff"]) if i % 2 == 0 else moe) for i in range(layers)]
+    return dict(architecture="Zikupel", vocab=DESIGN_VOCAB, width=s["width"], norm=dict(eps=1e-5), layers=zl)
+
+
 def design_configs(shape, layers):
     s = DESIGN_SHAPES[shape]
     mixer = dict(heads=s["heads"], dim=s["head"], vdim=s["head"], q_rank=s["q_rank"], kv_rank=s["kv_rank"],
@@ -564,12 +582,12 @@ def design_configs(shape, layers):
     qwen = dict(MODEL, vocab_size=DESIGN_VOCAB, hidden_size=s["width"], num_hidden_layers=layers,
                 num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["head"],
                 intermediate_size=s["ff"], tie_word_embeddings=False)
-    return {"zapipel": zap, "qwen2": qwen}
+    return {"zapipel": zap, "qwen2": qwen, "zikupel": zikupel_config(shape, layers)}
 
 
 def run_design(args):
     """Prefill (one 2,048-token prompt) and decode (``--batch`` requests at ``--context``; default 8 and 64 at
-    2,048) of the Zapipel design and of the Qwen2 decoder at equal sizes, random weights drawn on the device.
+    2,048) of the named design and of the Qwen2 decoder at equal sizes, random weights drawn on the device.
     Prints one JSON line; with ``--only`` and ``--arch`` one phase of one model (for a launch list)."""
     import torch
     import pico_vllm_b200  # noqa: F401
@@ -579,8 +597,8 @@ def run_design(args):
     context = args.context or 2048
     batches = [args.batch] if args.batch else [8, 64]
     shapes = sorted(DESIGN_SHAPES) if args.shape == "all" else [args.shape]
-    archs = ["zapipel", "qwen2"] if args.arch == "both" else [args.arch]
-    out = {"design": "zapipel", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+    archs = [args.design, "qwen2"] if args.arch == "both" else [args.arch]
+    out = {"design": args.design, "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
            "layers": layers, "vocab": DESIGN_VOCAB, "context": context, "peaks": pk["source"], "shapes": {}}
     sampler = ClockSampler()
     sampler.start()
@@ -592,7 +610,8 @@ def run_design(args):
             llm = LLM(model, dtype="bfloat16", page_size=16, num_pages=max_b * (context // 16 + 2) + 256, max_num_seqs=max_b,
                       max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=context + 64, use_cuda_graph=True)
             r = res[arch] = {"weight_GB": round(weight_bytes(llm.model) / 1e9, 3),
-                             "cache_bytes_per_token": kv_bytes_per_token(llm.model, llm.cache)}
+                             "cache_bytes_per_token": kv_bytes_per_token(llm.model, llm.cache),
+                             "state_bytes_per_request": sum(t[0].numel() * t.element_size() for t in llm.cache.states.values())}
             if args.only != "decode":
                 ms = prefill_phase(llm, 2048, reps=2 if args.only else 5, seed=3)
                 r["prefill_2048"] = {"ms": round(ms, 3), "tok_s": round(2048 / ms * 1e3)}
@@ -718,10 +737,11 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase only and print a short line (for profiling; not a bench value)")
-    ap.add_argument("--design", choices=["zapipel"], default=None,
+    ap.add_argument("--design", choices=["zapipel", "zikupel"], default=None,
                     help="the named design beside the Qwen2 decoder at equal sizes (prefill and decode); not the default run")
     ap.add_argument("--shape", choices=sorted(DESIGN_SHAPES) + ["all"], default="all", help="with --design: which sizes")
-    ap.add_argument("--arch", choices=["zapipel", "qwen2", "both"], default="both", help="with --design: which model")
+    ap.add_argument("--arch", choices=["zapipel", "zikupel", "qwen2", "both"], default="both",
+                    help="with --design: which model (both: the design and the Qwen2 decoder)")
     ap.add_argument("--micro", action="store_true",
                     help="time single decode kernels replayed from a graph (skinny products, decode attention)")
     ap.add_argument("--profile-range", choices=["decode", "prefill"], default=None,

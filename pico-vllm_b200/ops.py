@@ -90,7 +90,8 @@ def library():
         "pico_qk_norm_rope_store": [vp, i32, vp, vp, vp, f32, vp, vp, f32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                     i32, i32, vp],
         "pico_sigmoid_gate": [vp, vp, i32, i32, i32, i32, vp],
-        "pico_decay_linear_attention": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+        "pico_decay_linear_attention": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp,
+                                        i32, vp],
         "pico_gated_rms_norm": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
     }
     for name, args in sigs.items():
@@ -1004,12 +1005,17 @@ def sigmoid_gate(o: torch.Tensor, gate_logits: torch.Tensor) -> torch.Tensor:
 
 def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor,
                            state: torch.Tensor, seg_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor,
-                           heads: int, dim: int, vdim: int, act: int = 1) -> torch.Tensor:
+                           heads: int, dim: int, vdim: int, act: int = 1, max_q_len: int = 1,
+                           chunk: Optional[int] = None) -> torch.Tensor:
     """Linear attention with a decay per head: per head S <- decay * S + k_t v_t^T, o_t = S^T q_t, token by token in
     the order of each segment, from and into ``state`` float32 [slots, heads, vdim, dim] (row ``seg_slots[s]`` for
     segment s; S stored transposed).  q, k, v of a token lie in its row of ``proj`` at q_off + h * dim, k_off + h * dim,
     v_off + h * vdim and pass through silu (``act`` 1) or nothing (0) in float32.  A segment whose first position is
-    negative is padding.  Returns o float32 [T, heads * vdim]."""
+    negative is padding.  Returns o float32 [T, heads * vdim].
+
+    ``max_q_len``: the longest segment.  From LINEAR_CHUNK_MIN_TOKENS on the segments are cut into chunks of LINEAR_CHUNK
+    tokens that run side by side (local states, a scan over the chunks, then the outputs); ``chunk`` overrides that
+    policy (0: never)."""
     _cuda(proj, decay, state, seg_slots, cu_q, positions)
     T = proj.shape[0]
     S = seg_slots.shape[0]
@@ -1025,12 +1031,22 @@ def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: in
     if cu_q.shape[0] != S + 1 or positions.shape[0] != T:
         raise KernelError("decay_linear_attention: cu_q must have one more entry than seg_slots, positions one per token")
     out = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
+    if chunk is None:
+        chunk = LINEAR_CHUNK if max_q_len >= LINEAR_CHUNK_MIN_TOKENS else 0
+    chunk_state = None
+    if chunk > 0:
+        chunk_state = torch.empty((T // chunk + S) * heads * vdim * dim, dtype=torch.float32, device=proj.device)
     _check(library().pico_decay_linear_attention(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(state),
                                                  _ptr(seg_slots), _ptr(cu_q), _ptr(positions), _ptr(out), S, heads, dim,
-                                                 vdim, int(act), _dtype_code(proj), _stream()),
+                                                 vdim, int(act), int(chunk), int(max(max_q_len, 1)), _ptr(chunk_state),
+                                                 _dtype_code(proj), _stream()),
            f"decay_linear_attention (dim {dim})")
-    _count()
+    _count(3 if chunk > 0 else 1)
     return out
+
+
+LINEAR_CHUNK = 128                 # tokens per chunk of the chunked form of decay_linear_attention
+LINEAR_CHUNK_MIN_TOKENS = 256      # the longest segment of a step from which the chunked form is used
 
 
 def gated_rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], gate_logits: Optional[torch.Tensor], eps: float,

@@ -62,7 +62,7 @@ class DecayLinearAttention(Part):
         H, d, dv = self.heads, self.dim, self.vdim
         proj = _linear(h, self.proj_weight)                      # [T, q | k | v | (gate logits)]
         o = ops.decay_linear_attention(proj, 0, H * d, 2 * H * d, self.decay, cache.state, batch.seg_slots, batch.cu_q,
-                                       batch.positions, H, d, dv, self.act)
+                                       batch.positions, H, d, dv, self.act, max_q_len=max(batch.q_lens, default=1))
         g0 = 2 * H * d + H * dv
         y = ops.gated_rms_norm(o, self.out_norm, proj[:, g0:g0 + H * dv] if self.has_gate else None, self.eps, h.dtype)
         return _linear(y, self.o_weight)

@@ -342,7 +342,8 @@ def sigmoid_gate(o, gate_logits):
     return o
 
 
-def decay_linear_attention(proj, q_off, k_off, v_off, decay, state, seg_slots, cu_q, positions, heads, dim, vdim, act=1):
+def decay_linear_attention(proj, q_off, k_off, v_off, decay, state, seg_slots, cu_q, positions, heads, dim, vdim, act=1,
+                           max_q_len=1, chunk=None):
     T = proj.shape[0]
     p = proj.float()
     f = (lambda u: u * torch.sigmoid(u)) if act == 1 else (lambda u: u)

@@ -303,8 +303,10 @@ def test_norm_rotation_and_store_kernel(dtype, H, G, hd, norm_dim, rot, own_v):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,d,dv", [(3, 16, 24), (2, 128, 64), (1, 20, 12), (4, 32, 32), (2, 200, 40), (5, 64, 130)])
-def test_linear_attention_kernel(dtype, H, d, dv):
-    """Segments of 1, 2, 8, 9 and 70 tokens and a padding segment, from states that are not zero, into slots in any order."""
+@pytest.mark.parametrize("chunk", [0, 16, 3])
+def test_linear_attention_kernel(dtype, H, d, dv, chunk):
+    """Segments of 1, 2, 8, 9 and 70 tokens and a padding segment, from states that are not zero, into slots in any order;
+    walked token by token (chunk 0) or as chunks of 16 or 3 tokens side by side with a scan between them."""
     from pico_vllm_b200 import ops
     g = torch.Generator().manual_seed(d * 7 + dv)
     lens = [1, 70, 2, 9, 8, 1]
@@ -321,7 +323,7 @@ def test_linear_attention_kernel(dtype, H, d, dv):
     want = fake_ops.decay_linear_attention(proj, 4, 4 + H * d, 4 + 2 * H * d, decay, want_state, seg_slots, cu, pos, H, d, dv, 1)
     st = state.clone().to(DEV)
     got = ops.decay_linear_attention(proj.to(DEV), 4, 4 + H * d, 4 + 2 * H * d, decay.to(DEV), st, seg_slots.to(DEV),
-                                     cu.to(DEV), pos.to(DEV), H, d, dv, 1)
+                                     cu.to(DEV), pos.to(DEV), H, d, dv, 1, max_q_len=70, chunk=chunk)
     n = int(cu[5])
     _close(got[:n], want[:n], torch.float32, "outputs")
     _close(st, want_state, torch.float32, "states")
