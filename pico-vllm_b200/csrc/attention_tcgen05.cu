@@ -130,6 +130,11 @@ __device__ __forceinline__ float tca_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float tca_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tca_fence_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
 __device__ __forceinline__ void tca_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t acc) {
@@ -402,6 +407,9 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         float m_use = -INFINITY, l = 0.f;                    // maximum in use (log2 units), running sum
         bool dead = false;
         const uint64_t scale2 = tca_pack(scale_log2, scale_log2);
+        const float cap_t = cap_2x * 1.4426950408889634f;
+        const uint64_t cap_t2 = tca_pack(cap_t, cap_t), cap_m2 = tca_pack(-2.0f * cap_log2, -2.0f * cap_log2);
+        const uint64_t zero2 = tca_pack(0.f, 0.f), one2 = tca_pack(1.0f, 1.0f);
         int j = 0;
         for (int it = pipe; it < ntiles; it += 2, ++j) {
             const int n0 = (t_begin + it) * TCA_BN;
@@ -420,7 +428,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) tca_arrive(s_empty + pipe);       // this pipeline's next scores may be written
-            if (n0 + TCA_BN - 1 > pos0 || n0 < row_lo || n0 < lo) {      // some key may be hidden from some row
+            const bool edge = n0 + TCA_BN - 1 > pos0 || n0 < row_lo || n0 < lo;
+            if (edge) {      // some key may be hidden from some row
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int n = n0 + c;
@@ -454,9 +463,16 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
             for (int c = 0; c < 64; c += 2) {
                 float x0, x1;
                 if (CAP) {
-                    const float r0 = __uint_as_float(sv[c]), r1 = __uint_as_float(sv[c + 1]);
-                    x0 = r0 == -INFINITY ? -INFINITY : pico_score_log2(r0, scale_log2, cap_log2, cap_2x) + neg_m;
-                    x1 = r1 == -INFINITY ? -INFINITY : pico_score_log2(r1, scale_log2, cap_log2, cap_2x) + neg_m;
+                    // c log2e tanh(s / c) - m = (c log2e - m) - 2 c log2e / (2^(s * 2 log2e / c) + 1): one packed multiply, two
+                    // exponentials, one packed add, two reciprocals and one packed multiply-add for two scores
+                    float t0, t1, d0, d1;
+                    tca_unpack(tca_fma2(tca_pack(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), cap_t2, zero2), t0, t1);
+                    tca_unpack(tca_add2(tca_pack(tca_exp2(t0), tca_exp2(t1)), one2), d0, d1);
+                    tca_unpack(tca_fma2(tca_pack(tca_rcp(d0), tca_rcp(d1)), cap_m2, tca_pack(cap_log2 + neg_m, cap_log2 + neg_m)), x0, x1);
+                    if (edge) {          // a hidden key: 2^-inf + 1 = 1 would give it the weight of the lowest score
+                        if (sv[c] == 0xff800000u) x0 = -INFINITY;
+                        if (sv[c + 1] == 0xff800000u) x1 = -INFINITY;
+                    }
                 } else
                     tca_unpack(tca_fma2(tca_pack(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
                 const float p0 = tca_exp2(x0), p1 = tca_exp2(x1);

@@ -76,21 +76,44 @@ decay_linear_attention_kernel(const TA* __restrict__ proj, int row_stride, int q
             S[r][c] = (!STATE_ONLY && i < d && j < dv) ? st[(size_t)j * d + i] : 0.f;
         }
     float* mypart = part + (size_t)warp * LA_TOK * 32 * LA_COLS;
+    // The next eight tokens' q, k and v are asked for before the current eight are worked on and wait in registers
+    // (thread x holds elements x, x + 256, ... of the [8][d] tiles, DPL of them, and one v): the trip to memory hides
+    // behind the arithmetic instead of standing between two barriers.
+    TA rq[DPL], rk[DPL], rv;
+    auto fetch = [&](int t0) {
+        const int nt = min(LA_TOK, t_end - t0);
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            const int idx = threadIdx.x + e * (LA_WARPS * 32);
+            const int tt = idx / d, i = idx - tt * d;
+            if (tt < nt) {
+                const TA* row = proj + (size_t)(t0 + tt) * row_stride + (size_t)h * d + i;
+                if (!STATE_ONLY) rq[e] = row[q_off];
+                rk[e] = row[k_off];
+            }
+        }
+        const int tt = threadIdx.x / (LA_WARPS * LA_COLS), j = col_base + threadIdx.x % (LA_WARPS * LA_COLS);
+        if (tt < nt && j < dv) rv = proj[(size_t)(t0 + tt) * row_stride + v_off + (size_t)h * dv + j];
+    };
+    fetch(t_begin);
     for (int t0 = t_begin; t0 < t_end; t0 += LA_TOK) {
         const int nt = min(LA_TOK, t_end - t0);
         __syncthreads();                               // everyone is done with the tokens before
-        for (int idx = threadIdx.x; idx < nt * d; idx += blockDim.x) {
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            const int idx = threadIdx.x + e * (LA_WARPS * 32);
             const int tt = idx / d, i = idx - tt * d;
-            const TA* row = proj + (size_t)(t0 + tt) * row_stride + (size_t)h * d + i;
-            if (!STATE_ONLY) qs[tt * dp + i] = la_act(to_f32(row[q_off]), act);
-            ks[tt * dp + i] = la_act(to_f32(row[k_off]), act);
+            if (tt < nt) {
+                if (!STATE_ONLY) qs[tt * dp + i] = la_act(to_f32(rq[e]), act);
+                ks[tt * dp + i] = la_act(to_f32(rk[e]), act);
+            }
         }
-        for (int idx = threadIdx.x; idx < nt * LA_WARPS * LA_COLS; idx += blockDim.x) {
-            const int tt = idx / (LA_WARPS * LA_COLS), c = idx - tt * (LA_WARPS * LA_COLS);
-            const int j = col_base + c;
-            vs[idx] = j < dv ? la_act(to_f32(proj[(size_t)(t0 + tt) * row_stride + v_off + (size_t)h * dv + j]), act) : 0.f;
+        {
+            const int tt = threadIdx.x / (LA_WARPS * LA_COLS), j = col_base + threadIdx.x % (LA_WARPS * LA_COLS);
+            if (tt < nt) vs[threadIdx.x] = j < dv ? la_act(to_f32(rv), act) : 0.f;
         }
         __syncthreads();
+        if (t0 + LA_TOK < t_end) fetch(t0 + LA_TOK);
         for (int tt = 0; tt < nt; ++tt) {
             const float4 v4 = *reinterpret_cast<const float4*>(vs + tt * LA_WARPS * LA_COLS + warp * LA_COLS);
             const float vv[LA_COLS] = {v4.x, v4.y, v4.z, v4.w};
@@ -152,18 +175,21 @@ decay_linear_scan_kernel(const float* __restrict__ decay, float* __restrict__ st
     for (int i = 0; i < chunk; ++i) a_full *= a;
     float* sp = state + ((size_t)seg_slots[seg] * H + h) * (size_t)per_head + e;
     float* cs = chunk_state + ((size_t)la_chunk_base(cu_q, seg, chunk) * H + h) * (size_t)per_head + e;
+    const int n_last = t_end - t_begin - (n_chunks - 1) * chunk;
+    float a_last = 1.f;
+    for (int i = 0; i < n_last; ++i) a_last *= a;
+    const size_t step = (size_t)H * per_head;
     float S = *sp;
-    for (int c = 0; c < n_chunks; ++c) {
-        const int n = min(chunk, t_end - t_begin - c * chunk);
-        float an = a_full;
-        if (n < chunk) {
-            an = 1.f;
-            for (int i = 0; i < n; ++i) an *= a;
-        }
-        float* at = cs + (size_t)c * H * per_head;
-        const float local = *at;
-        *at = S;
-        S = fmaf(an, S, local);
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {          // the loads of eight chunks are in flight together
+        float local[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) local[k] = c0 + k < n_chunks ? cs[(size_t)(c0 + k) * step] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (c0 + k < n_chunks) {
+                cs[(size_t)(c0 + k) * step] = S;
+                S = fmaf(c0 + k == n_chunks - 1 ? a_last : a_full, S, local[k]);
+            }
     }
     *sp = S;
 }
