@@ -91,7 +91,7 @@ def library():
                                     i32, i32, vp],
         "pico_sigmoid_gate": [vp, vp, i32, i32, i32, i32, vp],
         "pico_decay_linear_attention": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp,
-                                        i32, vp],
+                                        vp, i32, i32, vp],
         "pico_gated_rms_norm": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
     }
     for name, args in sigs.items():
@@ -1033,19 +1033,20 @@ def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: in
     out = torch.empty((T, heads * vdim), dtype=torch.float32, device=proj.device)
     if chunk is None:
         chunk = LINEAR_CHUNK if max_q_len >= LINEAR_CHUNK_MIN_TOKENS else 0
-    chunk_state = None
+    chunk_state = prepared = None
     if chunk > 0:
         chunk_state = torch.empty((T // chunk + S) * heads * vdim * dim, dtype=torch.float32, device=proj.device)
+        prepared = torch.empty(T * heads * (2 * dim + vdim), dtype=torch.float32, device=proj.device)
     _check(library().pico_decay_linear_attention(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(state),
                                                  _ptr(seg_slots), _ptr(cu_q), _ptr(positions), _ptr(out), S, heads, dim,
                                                  vdim, int(act), int(chunk), int(max(max_q_len, 1)), _ptr(chunk_state),
-                                                 _dtype_code(proj), _stream()),
+                                                 _ptr(prepared), T, _dtype_code(proj), _stream()),
            f"decay_linear_attention (dim {dim})")
-    _count(3 if chunk > 0 else 1)
+    _count(4 if chunk > 0 else 1)
     return out
 
 
-LINEAR_CHUNK = 128                 # tokens per chunk of the chunked form of decay_linear_attention
+LINEAR_CHUNK = 64                  # tokens per chunk of the chunked form of decay_linear_attention
 LINEAR_CHUNK_MIN_TOKENS = 256      # the longest segment of a step from which the chunked form is used
 
 
