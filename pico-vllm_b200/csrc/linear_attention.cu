@@ -202,6 +202,32 @@ __global__ void la_prepare_kernel(const TA* __restrict__ proj, int row_stride, i
     }
 }
 
+// The same for bfloat16 rows with 16-byte loads: a thread takes eight neighbouring columns (every offset, size and stride a
+// multiple of 8, so that the eight lie in one of q, k, v and on a 16-byte boundary).
+__global__ void la_prepare_bf16x8_kernel(const bf16* __restrict__ proj, int row_stride, int q_off, int k_off, int v_off,
+                                         int nqk, int nv, int act, size_t total8, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n8 = (2 * nqk + nv) / 8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / n8;
+        const int c = (int)(idx - t * n8) * 8;
+        const int src = c < nqk ? q_off + c : c < 2 * nqk ? k_off + (c - nqk) : v_off + (c - 2 * nqk);
+        const uint4 raw = *reinterpret_cast<const uint4*>(proj + t * row_stride + src);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 v = __bfloat1622float2(h2[k]);
+            f[2 * k] = la_act(v.x, act);
+            f[2 * k + 1] = la_act(v.y, act);
+        }
+        float4* dst = reinterpret_cast<float4*>(out + t * (size_t)(n8 * 8) + c);
+        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+
 // Pass B: a thread per state element of one (segment, head); walks the segment's chunks in order.
 __global__ void __launch_bounds__(256)
 decay_linear_scan_kernel(const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ seg_slots,
@@ -284,10 +310,16 @@ PICO_API int pico_decay_linear_attention(const void* proj, int row_stride, int q
         const long long cap = 16LL * pico_num_sms();
         const size_t want = (total + 255) / 256;
         const int blocks = (int)((long long)want > cap ? cap : (long long)want);
+        const bool vec8 = dtype == PICO_BF16 && nqk % 8 == 0 && nv % 8 == 0 && row_stride % 8 == 0 && q_off % 8 == 0 &&
+                          k_off % 8 == 0 && v_off % 8 == 0 && ((uintptr_t)proj & 15) == 0 && ((uintptr_t)prepared & 15) == 0;
         if (dtype == PICO_F32)
             pico_launch((la_prepare_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)proj, row_stride, q_off,
                         k_off, v_off, nqk, nv, act, total, prepared);
-        else
+        else if (vec8) {
+            const size_t want8 = (total / 8 + 255) / 256;
+            pico_launch(la_prepare_bf16x8_kernel, dim3((int)((long long)want8 > cap ? cap : (long long)want8)), dim3(256), 0, stream,
+                        (const bf16*)proj, row_stride, q_off, k_off, v_off, nqk, nv, act, total / 8, prepared);
+        } else
             pico_launch((la_prepare_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, (const bf16*)proj, row_stride, q_off,
                         k_off, v_off, nqk, nv, act, total, prepared);
         proj = prepared;

@@ -578,6 +578,27 @@ __global__ void moe_scaled_act_kernel(const TA* u, const int* __restrict__ perm,
     }
 }
 
+// bfloat16 rows of a multiple of 8 elements, 16 bytes per access.
+__global__ void moe_scaled_act_bf16x8_kernel(const bf16* u, const int* __restrict__ perm, const float* __restrict__ wgt, int ff8,
+                                             size_t total8, int act_kind, bf16* out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = idx / ff8;
+        const float w = wgt ? wgt[perm ? perm[p] : p] : 1.0f;
+        const uint4 raw = *reinterpret_cast<const uint4*>(u + idx * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint4 res;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 v = __bfloat1622float2(h2[k]);
+            o2[k] = __floats2bfloat162_rn(moe_act(w * v.x, act_kind), moe_act(w * v.y, act_kind));
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = res;
+    }
+}
+
 PICO_API int pico_moe_scaled_act(const void* u, const int* perm, const float* wgt, int n, int ff, int act_kind, void* out,
                                  int dtype, cudaStream_t stream) {
     if (n <= 0 || ff <= 0) return 0;
@@ -589,7 +610,11 @@ PICO_API int pico_moe_scaled_act(const void* u, const int* perm, const float* wg
     if (dtype == PICO_F32)
         pico_launch((moe_scaled_act_kernel<float>), dim3(blocks), dim3(256), 0, stream, (const float*)u, perm, wgt, ff, total,
                     act_kind, (float*)out);
-    else if (dtype == PICO_BF16)
+    else if (dtype == PICO_BF16 && ff % 8 == 0 && ((uintptr_t)u & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        const size_t want8 = (total / 8 + 255) / 256;
+        pico_launch(moe_scaled_act_bf16x8_kernel, dim3((int)((long long)want8 > cap ? cap : (long long)want8)), dim3(256), 0, stream,
+                    (const bf16*)u, perm, wgt, ff / 8, total / 8, act_kind, (bf16*)out);
+    } else if (dtype == PICO_BF16)
         pico_launch((moe_scaled_act_kernel<bf16>), dim3(blocks), dim3(256), 0, stream, (const bf16*)u, perm, wgt, ff, total,
                     act_kind, (bf16*)out);
     else

@@ -246,6 +246,9 @@ def test_a_state_that_remembers_the_first_tokens(dtype):
     steps += helpers.trace_mixed({"x": reqs["x"], "y": reqs["y"]}, max_live=2, seed=5, chunk_sizes=(2, 7, 64, 3, 2, 33))
     runner = _runner(raw, tensors, dtype, 1024, max_num_seqs=2)
     _compare(steps, reqs, helpers.replay(runner, steps), logits, dtype, f"state/{dtype}")
+    # whole prompts of 500 and 300 tokens: the chunks of a long portion run side by side with a scan between them
+    steps = helpers.trace_whole({"x": reqs["x"], "y": reqs["y"]}) + helpers.trace_portions({"x": reqs["x"]}, sizes=(300, 2, 198))
+    _compare(steps, reqs, helpers.replay(runner, steps), logits, dtype, f"long portions/{dtype}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -304,7 +307,8 @@ def test_norm_rotation_and_store_kernel(dtype, H, G, hd, norm_dim, rot, own_v):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,d,dv", [(3, 16, 24), (2, 128, 64), (1, 20, 12), (4, 32, 32), (2, 200, 40), (5, 64, 130)])
 @pytest.mark.parametrize("chunk", [0, 16, 3])
-def test_linear_attention_kernel(dtype, H, d, dv, chunk):
+@pytest.mark.parametrize("off", [4, 8])
+def test_linear_attention_kernel(dtype, H, d, dv, chunk, off):
     """Segments of 1, 2, 8, 9 and 70 tokens and a padding segment, from states that are not zero, into slots in any order;
     walked token by token (chunk 0) or as chunks of 16 or 3 tokens side by side with a scan between them."""
     from pico_vllm_b200 import ops
@@ -315,14 +319,14 @@ def test_linear_attention_kernel(dtype, H, d, dv, chunk):
     pos = torch.arange(T, dtype=torch.int32)
     pos[cu[5]:] = -1                                             # the last segment is padding
     seg_slots = torch.tensor([4, 0, 6, 2, 5, 0], dtype=torch.int32)
-    width = H * (2 * d + dv) + 8
+    width = H * (2 * d + dv) + 16
     proj = (torch.randn(T, width, generator=g) * 0.7).to(dtype)
     decay = torch.rand(H, generator=g) * 0.5 + 0.5
     state = torch.randn(7, H, dv, d, generator=g) * 0.3
     want_state = state.clone()
-    want = fake_ops.decay_linear_attention(proj, 4, 4 + H * d, 4 + 2 * H * d, decay, want_state, seg_slots, cu, pos, H, d, dv, 1)
+    want = fake_ops.decay_linear_attention(proj, off, off + H * d, off + 2 * H * d, decay, want_state, seg_slots, cu, pos, H, d, dv, 1)
     st = state.clone().to(DEV)
-    got = ops.decay_linear_attention(proj.to(DEV), 4, 4 + H * d, 4 + 2 * H * d, decay.to(DEV), st, seg_slots.to(DEV),
+    got = ops.decay_linear_attention(proj.to(DEV), off, off + H * d, off + 2 * H * d, decay.to(DEV), st, seg_slots.to(DEV),
                                      cu.to(DEV), pos.to(DEV), H, d, dv, 1, max_q_len=70, chunk=chunk)
     n = int(cu[5])
     _close(got[:n], want[:n], torch.float32, "outputs")
