@@ -556,7 +556,7 @@ def zikupel_config(shape, layers):
     s = DESIGN_SHAPES[shape]
     H, d = s["heads"], s["head"]
     att = dict(heads=H, kv_heads=s["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, softcap=30.0,
-               rot=dict(base=10000.0, dims=d // 2, scaling=dict(factor=4.0, original=1024, fast=32.0, slow=1.0)))
+               rot=dict(base=10000.0, dims=d // 2, scaling=dict(factor=8.0, original=1024, fast=16.0, slow=2.0)))
     lin = dict(heads=H, dim=d, vdim=d, decay=[math.exp(-2.0 ** (-1 - 8.0 * h / H)) for h in range(H)])
     moe = dict(kind="moe", expert=dict(ff=s["ff"] // s["top"]), router=dict(experts=s["experts"], top=s["top"]),
                shared=dict(ff=s["ff"] // s["top"]))

@@ -67,7 +67,7 @@ SHAPES = {
     # the head sizes the tensor-core kernels take (64 and 128): 8 query heads on one kv head, 3 on 3; a linear mixer with
     # keys of 128; 1 of 4 experts
     "b": dict(architecture="Zikupel", vocab=300, width=128, norm=dict(eps=1e-6),
-              layers=[_layer(_att(8, 1, 64, 0.25, 32, 20000.0, softcap=15.0, scaling=(4.0, 64, 16.0, 1.0)), _moe(64, 4, 1, shared=64)),
+              layers=[_layer(_att(8, 1, 64, 0.25, 32, 30000.0, softcap=15.0, scaling=(3.0, 64, 16.0, 1.5)), _moe(64, 4, 1, shared=64)),
                       _layer(_lin(2, 128, 64, (0.999, 0.7)), dict(kind="dense", ff=160)),
                       _layer(_att(3, 3, 128, 0.15, 128, 1000.0), _moe(32, 6, 3))]),
     # awkward sizes: a width that is a multiple of 4 only, an odd vocabulary, heads of 24 and 40 (padded to 32 and 48 in
@@ -77,8 +77,13 @@ SHAPES = {
               layers=[_layer(_att(5, 5, 24, 0.4, 6, 300.0, softcap=10.0), _moe(28, 7, 3, shared=20)),
                       _layer(_lin(1, 20, 12, (0.9,)), dict(kind="dense", ff=52)),
                       _layer(_att(6, 2, 40, 0.3, 40, 777.0, scaling=(2.0, 16, 4.0, 0.5)), None)]),
+    # sizes that are multiples of 2 at most: width 90, heads of 16 with 4 dims turned, a linear mixer with keys of 8 and values
+    # of 4, inner sizes 14, 10 and 6, one of two experts
+    "d": dict(architecture="Zikupel", vocab=101, width=90, norm=dict(eps=1e-5),
+              layers=[_layer(_lin(2, 8, 4, (0.9, 0.6)), _moe(10, 2, 1, shared=6)),
+                      _layer(_att(3, 1, 16, 0.5, 4, 50.0, softcap=8.0), dict(kind="dense", ff=14))]),
 }
-SEEDS = {"a": 11, "b": 22, "c": 35}     # c: a seed without a token whose tiny sublayer output the post-norm blows up in bfloat16
+SEEDS = {"a": 11, "b": 22, "c": 35, "d": 44}     # c: a seed without a token whose tiny sublayer output the post-norm blows up in bfloat16
 STD = 0.12      # weights large enough that attention and routers are far from uniform
 
 
@@ -128,11 +133,11 @@ def _compare(steps, reqs, got, logits, dtype, what):
 
 _CUTS = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_tail_decode(r, 32),
          "portions": helpers.trace_portions, "mixed": lambda r: helpers.trace_mixed(r, max_live=4, seed=3)}
-LENGTHS = {"a": [1, 9, 33, 70, 150, 230], "b": [2, 17, 48, 97, 200], "c": [3, 40, 129, 75]}
+LENGTHS = {"a": [1, 9, 33, 70, 150, 230], "b": [2, 17, 48, 97, 200], "c": [3, 40, 129, 75], "d": [5, 60, 300]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 @pytest.mark.parametrize("cut,graph", [("whole", False), ("tail", False), ("tail", True), ("portions", False),
                                        ("mixed", False), ("mixed", True)])
 def test_every_cutting_matches_plain(dtype, name, cut, graph):
@@ -389,7 +394,7 @@ def test_ungated_experts_kernels(dtype, T, D, ff, experts, top, on_input):
     _close(ops.activation(u.clone().to(DEV), ops.MOE_ACT_RELU2), fake_ops.activation(u.clone(), 1), dtype, "relu squared")
 
 
-@pytest.mark.parametrize("hd,H,G,ps", [(64, 8, 1, 16), (128, 6, 2, 16), (32, 4, 2, 8), (128, 3, 3, 64), (48, 6, 2, 4)])
+@pytest.mark.parametrize("hd,H,G,ps", [(64, 8, 1, 16), (128, 10, 2, 16), (32, 4, 2, 8), (128, 3, 3, 64), (48, 6, 3, 4)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_attention_kernels_with_capped_scores(dtype, hd, H, G, ps):
     """Prompt portions and single tokens in one batch through the kernels the mixer uses (tensor cores in bfloat16 - with
