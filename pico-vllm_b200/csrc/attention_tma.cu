@@ -98,7 +98,8 @@ __device__ __forceinline__ uint32_t tile_off(int key, int dim, int page_size) {
 // with stage s.
 // CW consumer warps in groups of four: group i takes tiles i, i + CW/4, ... (a group multiplies one tile,
 // 16 cache positions per warp); one group is what the launcher uses.
-template <int HD, int TMA_STAGES, int CW, int NT>     // head size 64 or 128; stages; consumer warps (4 or 8); 8-head tiles (g <= 8 NT)
+// CAP: scores pass through a soft cap (cap_log2, cap_2x as for pico_score_log2); without it the kernel is what it was
+template <int HD, int TMA_STAGES, int CW, int NT, bool CAP>     // head size 64 or 128; stages; consumer warps (4 or 8); 8-head tiles (g <= 8 NT)
 __global__ void __launch_bounds__((CW + 1) * 32)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
@@ -281,7 +282,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float v = (sc[nt][0][e] + sc[nt][1][e]) + (sc[nt][2][e] + sc[nt][3][e]);
-                    x[e] = ((e < 2) ? vis_a : vis_b) ? pico_score_log2(v, scale_log2, cap_log2, cap_2x) : -INFINITY;
+                    x[e] = ((e < 2) ? vis_a : vis_b) ? (CAP ? pico_score_log2(v, scale_log2, cap_log2, cap_2x) : v * scale_log2) : -INFINITY;
                 }
                 float p[4];
 #pragma unroll
@@ -478,14 +479,14 @@ int pico_launch_decode_combine(const float* part_o, const float* part_ml, void* 
                                int nh, int hd, int n_splits, cudaStream_t stream);
 
 // Can clusters of `size` blocks of the decode kernel run here?  (Asked once per configuration.)
-template <int HD, int ST, int CW, int NT>
+template <int HD, int ST, int CW, int NT, bool CAP>
 static bool tma_cluster_query(int size, size_t smem) {
-    if (size > 8 && cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW, NT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+    if (size > 8 && cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW, NT, CAP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
                         cudaSuccess) {
         cudaGetLastError();
         return false;
     }
-    cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW, NT, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(size, 1, 1);
     cfg.blockDim = dim3((CW + 1) * 32);
@@ -498,21 +499,22 @@ static bool tma_cluster_query(int size, size_t smem) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, paged_decode_tma_kernel<HD, ST, CW, NT>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, paged_decode_tma_kernel<HD, ST, CW, NT, CAP>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
     return n > 0;
 }
+template <bool CAP>
 static bool tma_cluster_ok(int hd, int size, int nt, size_t smem) {
-    static int cache[2][2][5];      // [hd 64/128][head tiles - 1][log2 size]: 0 unknown, 1 yes, 2 no
+    static int cache[2][2][5];      // [hd 64/128][head tiles - 1][log2 size]: 0 unknown, 1 yes, 2 no (one table per CAP)
     int lg = 0;
     while ((1 << lg) < size) ++lg;
     int& c = cache[hd == 128 ? 1 : 0][nt - 1][lg];
     if (c == 0) {
         bool ok;
-        if (hd == 128) ok = nt == 1 ? tma_cluster_query<128, TMA_STAGES_MANY, 4, 1>(size, smem) : tma_cluster_query<128, TMA_STAGES_MANY, 4, 2>(size, smem);
-        else ok = nt == 1 ? tma_cluster_query<64, TMA_STAGES_MANY, 4, 1>(size, smem) : tma_cluster_query<64, TMA_STAGES_MANY, 4, 2>(size, smem);
+        if (hd == 128) ok = nt == 1 ? tma_cluster_query<128, TMA_STAGES_MANY, 4, 1, CAP>(size, smem) : tma_cluster_query<128, TMA_STAGES_MANY, 4, 2, CAP>(size, smem);
+        else ok = nt == 1 ? tma_cluster_query<64, TMA_STAGES_MANY, 4, 1, CAP>(size, smem) : tma_cluster_query<64, TMA_STAGES_MANY, 4, 2, CAP>(size, smem);
         c = ok ? 1 : 2;
     }
     return c == 1;
@@ -547,16 +549,20 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
     // 2, 4, 8 or 16 splits: the splits of one (token, kv head) run as one thread-block cluster and are
     // added through distributed shared memory; otherwise through scratch and the combine kernel
     int cluster = 0;
-    if (n_splits == 2 || n_splits == 4 || n_splits == 8 || n_splits == 16) cluster = tma_cluster_ok(hd, n_splits, nt, smem) ? 1 : 0;
+    if (n_splits == 2 || n_splits == 4 || n_splits == 8 || n_splits == 16) cluster = (cap_log2 > 0.f ? tma_cluster_ok<true>(hd, n_splits, nt, smem) : tma_cluster_ok<false>(hd, n_splits, nt, smem)) ? 1 : 0;
     if (n_splits > 1 && !cluster && (!part_o || !part_ml)) return PICO_ERR_SIZE;
-#define LAUNCH_TMA(HD, NT)                                                                                              \
+#define LAUNCH_TMA_C(HD, NT, CAP)                                                                                       \
     do {                                                                                                                \
-        cudaFuncSetAttribute(paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+        cudaFuncSetAttribute(paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                              (int)smem);                                                                                \
-        pico_launch_cluster((paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT>), grid, dim3(5 * 32), smem, stream,    \
+        pico_launch_cluster((paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT, CAP>), grid, dim3(5 * 32), smem, stream, \
                             cluster ? n_splits : 1, km, vm, (const bf16*)q, q_row_stride, (bf16*)out, part_o,           \
                             part_ml, tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, page_size,       \
                             window, scale_log2, n_splits, cluster, kv_same, cap_log2, cap_2x);                          \
+    } while (0)
+#define LAUNCH_TMA(HD, NT)                                                                                              \
+    do {                                                                                                                \
+        if (cap_log2 > 0.f) LAUNCH_TMA_C(HD, NT, true); else LAUNCH_TMA_C(HD, NT, false);                               \
     } while (0)
     if (hd == 64) {
         if (nt == 1) LAUNCH_TMA(64, 1); else LAUNCH_TMA(64, 2);
@@ -564,6 +570,7 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
         if (nt == 1) LAUNCH_TMA(128, 1); else LAUNCH_TMA(128, 2);
     }
 #undef LAUNCH_TMA
+#undef LAUNCH_TMA_C
     if (n_splits > 1 && !cluster)
         return pico_launch_decode_combine(part_o, part_ml, out, tok_list, n_tok, nh, hd, n_splits, stream);
     return pico_launch_status();
