@@ -389,12 +389,68 @@ __global__ void __launch_bounds__(256) gated_rms_norm_kernel(const float* __rest
     }
 }
 
+// A block per row, every access four elements wide (N, g_stride and the pointers allow it): a thread's float4 loads of x
+// and its loads of the gate logits and the weight are all asked for before anything is waited for - a row of a few
+// thousand elements is one or two trips to memory, which is what a step of a handful of tokens is made of.
+template <typename TA>
+__global__ void __launch_bounds__(256) gated_rms_norm_row4_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                  const TA* __restrict__ g, int g_stride, float eps,
+                                                                  TA* __restrict__ y, int N) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    constexpr int MAXV = 4;                              // float4 per thread: N <= 4 * 256 * MAXV
+    const size_t t = blockIdx.x;
+    const float* row = x + t * N;
+    const TA* gr = g ? g + t * g_stride : nullptr;
+    float4 v[MAXV], ww[MAXV], gg[MAXV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+        const int i = (threadIdx.x + k * 256) * 4;
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < N) {
+            v[k] = *reinterpret_cast<const float4*>(row + i);
+            ww[k] = w ? *reinterpret_cast<const float4*>(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+            if (gr) gg[k] = make_float4(to_f32(gr[i]), to_f32(gr[i + 1]), to_f32(gr[i + 2]), to_f32(gr[i + 3]));
+        }
+        ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)N + eps);
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+        const int i = (threadIdx.x + k * 256) * 4;
+        if (i >= N) continue;
+        float o[4] = {v[k].x * inv * ww[k].x, v[k].y * inv * ww[k].y, v[k].z * inv * ww[k].z, v[k].w * inv * ww[k].w};
+        if (gr) {
+            o[0] /= 1.0f + expf(-gg[k].x);
+            o[1] /= 1.0f + expf(-gg[k].y);
+            o[2] /= 1.0f + expf(-gg[k].z);
+            o[3] /= 1.0f + expf(-gg[k].w);
+        }
+        TA* dst = y + t * N + i;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dst[e] = from_f32<TA>(o[e]);
+    }
+}
+
 PICO_API int pico_gated_rms_norm(const float* x, const float* w, const void* g, int g_stride, float eps, void* y, int T,
                                  int N, int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (N < 1) return PICO_ERR_SIZE;
     const dim3 grid((T + 7) / 8);
     const bool vec = N % 4 == 0;
+    if (vec && N <= 4096 && T <= 4096) {             // few rows: a block per row
+        if (dtype == PICO_F32)
+            pico_launch((gated_rms_norm_row4_kernel<float>), dim3(T), dim3(256), 0, stream, x, w, (const float*)g, g_stride, eps,
+                        (float*)y, N);
+        else if (dtype == PICO_BF16)
+            pico_launch((gated_rms_norm_row4_kernel<bf16>), dim3(T), dim3(256), 0, stream, x, w, (const bf16*)g, g_stride, eps,
+                        (bf16*)y, N);
+        else
+            return PICO_ERR_DTYPE;
+        return pico_launch_status();
+    }
 #define GN_LAUNCH(TA, V)                                                                                              \
     pico_launch((gated_rms_norm_kernel<TA, V>), grid, dim3(256), 0, stream, x, w, (const TA*)g, g_stride, eps, (TA*)y, T, N)
     if (dtype == PICO_F32) {
