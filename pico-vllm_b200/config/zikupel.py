@@ -7,7 +7,7 @@ keys: ``vocab``, ``width``, ``norm.eps``.  Mixer kinds:
 * ``attention`` - ``heads``, ``kv_heads``, ``dim`` (query/key size per head), ``vdim`` (value size per head; the values
   are the keys, so it equals ``dim``), ``scale`` (the factor on q.k), ``softcap`` (optional; scores pass through
   softcap * tanh(s / softcap)), ``rot`` = ``{"base", "dims", "scaling": {"factor", "original", "fast", "slow"} or absent}``.
-* ``lightning`` - ``heads``, ``dim``, ``vdim``, ``decay`` (one number per head).
+* ``lightning`` - ``heads``, ``dim``, ``vdim``, ``decay`` (one number per head; a single number stands for all heads).
 
 Feed-forward: ``{"kind": "dense", "ff": n}`` or ``{"kind": "moe", "expert": {"ff": n}, "router": {"experts": E, "top": k},
 "shared": {"ff": m} or absent}``.
@@ -188,6 +188,8 @@ def _read_lightning(raw, at: str) -> LightningSpec:
     m = _object(raw, at)
     heads = m.integer("heads", minimum=1)
     decay = m.any("decay")
+    if isinstance(decay, (int, float)) and not isinstance(decay, bool):
+        decay = [decay] * heads                   # one number: the same decay for every head
     if not isinstance(decay, list) or len(decay) != heads or any(isinstance(a, bool) or not isinstance(a, (int, float))
                                                                  for a in decay):
         raise ConfigError(f"{at}: 'decay' must be a list of {heads} numbers, one per head")

@@ -21,6 +21,9 @@ def test_round_trip_and_fields():
     att = cfg.layers[1].mixer
     assert (att.rot.dims, att.rot.scaling.factor, att.softcap) == (16, 8.0, 6.0) and cfg.layers[2].mixer.rot.scaling is None
     assert cfg.layers[2].mixer.softcap is None
+    one = copy.deepcopy(SHAPES["a"])
+    one["layers"][0]["mixer"]["decay"] = 0.75                  # a single number stands for all heads
+    assert config_from_dict(one).layers[0].mixer.decay == (0.75, 0.75, 0.75)
 
 
 @pytest.mark.parametrize("edit,word", [
