@@ -340,6 +340,32 @@ def test_linear_attention_kernel(dtype, H, d, dv, chunk, off):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,d,dv", [(3, 16, 24), (2, 128, 64), (1, 20, 12), (2, 200, 40), (5, 64, 130), (2, 30, 8)])
+def test_linear_attention_of_single_tokens(dtype, H, d, dv):
+    """A step in which every segment brings one token (a decode step: a stream of states): slots in any order, a padding
+    row, states that are not zero."""
+    from pico_vllm_b200 import ops
+    g = torch.Generator().manual_seed(d * 3 + dv)
+    S = 9
+    cu = torch.arange(S + 1, dtype=torch.int32)
+    pos = torch.randint(0, 500, (S,), generator=g).to(torch.int32)
+    pos[6] = -1
+    seg_slots = torch.tensor([4, 0, 6, 2, 5, 9, 0, 1, 8], dtype=torch.int32)
+    proj = (torch.randn(S, H * (2 * d + dv) + 8, generator=g) * 0.7).to(dtype)
+    decay = torch.rand(H, generator=g) * 0.5 + 0.5
+    state = torch.randn(10, H, dv, d, generator=g) * 0.3
+    want_state = state.clone()
+    want = fake_ops.decay_linear_attention(proj, 0, H * d, 2 * H * d, decay, want_state, seg_slots, cu, pos, H, d, dv, 1)
+    st = state.clone().to(DEV)
+    got = ops.decay_linear_attention(proj.to(DEV), 0, H * d, 2 * H * d, decay.to(DEV), st, seg_slots.to(DEV), cu.to(DEV),
+                                     pos.to(DEV), H, d, dv, 1, max_q_len=1)
+    live = pos >= 0
+    _close(got[live], want[live], torch.float32, "outputs")
+    _close(st, want_state, torch.float32, "states")
+    assert torch.equal(st[3].cpu(), state[3]) and torch.equal(st[7].cpu(), state[7])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("N", [48, 130, 1024, 4100])
 def test_gated_norm_and_gate_kernels(dtype, N):
     from pico_vllm_b200 import ops
